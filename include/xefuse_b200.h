@@ -1,0 +1,219 @@
+/*
+ * xefuse_b200 — C ABI of the B200 (sm_100a) fused GEMM + epilogue library.
+ *
+ * This is the boundary the header-only C++ front end (xe_fuse::builder::MakeGemm<...>::Gemm,
+ * xe_fuse::Gemm* named kernels, xe_fuse::standalone::*) calls into.  Everything is plain C:
+ * POD structs, raw device pointers, sizes, a cudaStream_t passed as void*.  No C++ or torch
+ * types cross it, nothing throws across it, every entry returns an xf_status.
+ *
+ * Reference interfaces each entry replaces (paths inside IntelLabs/Xe-Fuse):
+ *   xf_gemm_can_implement   <- GemmUniversalAdapter::can_implement(args)
+ *                              (include/xe-fuse/builder/epilogue_builder.hpp:378-381, tests/test_k1.cpp:99)
+ *   xf_gemm_workspace_size  <- GemmUniversalAdapter::get_workspace_size(args)   (tests/test_k1.cpp:96)
+ *   xf_gemm_plan_create     <- GemmUniversalAdapter::initialize(args, workspace) (tests/test_k1.cpp:100)
+ *   xf_gemm_run             <- GemmUniversalAdapter::run()                       (tests/test_k1.cpp:101)
+ *   xf_epilogue_desc        <- the EVT::Arguments tree of the builder aliases
+ *                              (include/xe-fuse/builder/epilogue_builder.hpp:58-280)
+ *   xf_sa_*                 <- xe_fuse::standalone::* (include/xe-fuse/standalone/ops.hpp:32-354)
+ *   xf_compute_rstd*        <- xe_fuse::launch_compute_rstd / launch_compute_rstd_and_quantize
+ *                              (include/xe-fuse/kernels/compute_rstd.hpp:12-125)
+ *
+ * Memory layout (all row-major, the reference's convention, tests/test_k1.cpp:54-64):
+ *   A [L][M][K]  (K contiguous)       bf16 or int8
+ *   B [L][K][N]  (N contiguous)       bf16 or int8   -- note: N-contiguous weights
+ *   D [L][M][Nout] (Nout contiguous)  bf16 (or fp32 / int32 "raw accumulator" output)
+ * Leading dimensions are in elements.  A batch stride of 0 shares one matrix across L.
+ */
+#ifndef XEFUSE_B200_H_
+#define XEFUSE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define XF_API
+#else
+#define XF_API __attribute__((visibility("default")))
+#endif
+
+/* Status codes.  Values mirror cutlass::Status so the front end can cast 1:1. */
+typedef enum xf_status {
+  XF_SUCCESS = 0,
+  XF_ERR_MISALIGNED_OPERAND = 1,
+  XF_ERR_INVALID_DATA_TYPE = 2,
+  XF_ERR_INVALID_LAYOUT = 3,
+  XF_ERR_INVALID_PROBLEM = 4,
+  XF_ERR_NOT_SUPPORTED = 5,
+  XF_ERR_WORKSPACE_NULL = 6,
+  XF_ERR_INTERNAL = 7,
+  XF_ERR_ARCH_MISMATCH = 8,
+  XF_ERR_INSUFFICIENT_DRIVER = 9,
+  XF_ERR_MEMORY_ALLOCATION = 10,
+  XF_INVALID = 11
+} xf_status;
+
+typedef enum xf_dtype {
+  XF_DT_BF16 = 0,
+  XF_DT_S8 = 1,
+  XF_DT_F32 = 2,
+  XF_DT_S32 = 3
+} xf_dtype;
+
+/* Unary activation applied after the affine steps
+ * (functors of include/xe-fuse/visitors/xe_elementwise_compute.hpp:53-89). */
+typedef enum xf_unary {
+  XF_UNARY_NONE = 0,
+  XF_UNARY_GELU = 1,      /* x*0.5*(1+erf(x/sqrt2)) */
+  XF_UNARY_GELU_TANH = 2, /* tanh approximation       */
+  XF_UNARY_SILU = 3,      /* x/(1+exp(-x))            */
+  XF_UNARY_RELU = 4,
+  XF_UNARY_SIGMOID = 5,
+  XF_UNARY_EXP = 6
+} xf_unary;
+
+/* Operation on adjacent column pairs (2k, 2k+1)
+ * (include/xe-fuse/visitors/xe_pairwise_compute.hpp:71-89, xe_rope_compute.hpp:51-59). */
+typedef enum xf_pair {
+  XF_PAIR_NONE = 0,
+  XF_PAIR_SWIGLU = 1, /* silu(x[2k]) * x[2k+1] */
+  XF_PAIR_GEGLU = 2,  /* gelu(x[2k]) * x[2k+1] */
+  XF_PAIR_ROPE = 3,   /* e' = e*c + o*s ; o' = -e*s + o*c */
+  XF_PAIR_SWAP = 4    /* each column takes its partner's value */
+} xf_pair;
+
+/* Where the pair result goes. */
+typedef enum xf_out_layout {
+  XF_OUT_FULL = 0,    /* D is [M,N]; pair ops that yield one value per pair write it to both columns
+                         (what the reference's K2 does, tests/test_k2.cpp:4-5) */
+  XF_OUT_COMPACT = 1  /* D is [M,N/2]; one value per pair (SwiGLU/GeGLU only) */
+} xf_out_layout;
+
+/* A broadcast vector operand: v[m] (per output row) or v[n] (per output column). */
+typedef struct xf_vec {
+  const void* ptr;        /* device pointer; NULL => null_default is used for every element */
+  int32_t dtype;          /* XF_DT_F32 or XF_DT_BF16 */
+  int32_t enabled;        /* 0 => step skipped */
+  int64_t batch_stride;   /* elements between batches (dCol/dRow's third mode) */
+  float null_default;
+  int32_t pad_;
+} xf_vec;
+
+/* A full [M,N] operand (AuxLoad / AuxStore). */
+typedef struct xf_mat {
+  const void* ptr;        /* device pointer */
+  int32_t dtype;          /* XF_DT_BF16 or XF_DT_F32 */
+  int32_t enabled;
+  int64_t ld;             /* elements between rows */
+  int64_t batch_stride;   /* elements between batches */
+} xf_mat;
+
+/*
+ * Flat epilogue program.  Every supported visitor tree lowers to this fixed order, each step
+ * optional; v starts as float(acc):
+ *   1. v += residual[m,n]            (AddResidual)
+ *   2. aux_store[m,n] = v            (DualOutput's AuxStore; second output)
+ *   3. v *= row_scale[m]             (ScaleRows / per-token scale)
+ *   4. v *= col_scale[n]             (ScaleCols / per-channel scale)
+ *   5. v += bias[n]                  (BiasAdd)
+ *   6. v = unary(v)
+ *   7. pair op on columns (2k,2k+1); RoPE takes c,s = cos_sin[m, 2k], cos_sin[m, 2k+1]
+ *   8. D = round-to-nearest-even(v)
+ */
+typedef struct xf_epilogue_desc {
+  xf_mat residual;
+  xf_mat aux_store;       /* ptr is written; dtype bf16 */
+  xf_vec row_scale;
+  xf_vec col_scale;
+  xf_vec bias;
+  int32_t unary;          /* xf_unary */
+  int32_t pair;           /* xf_pair */
+  xf_mat cos_sin;         /* fp32; ld = row pitch in elements */
+  int32_t cos_sin_period; /* 0: table spans all N columns (reference form).  P>0: column n reads
+                             cos_sin[m, n % P] (one head_dim-wide table shared by all heads);
+                             P must be a multiple of 32 */
+  int32_t out_layout;     /* xf_out_layout */
+} xf_epilogue_desc;
+
+typedef struct xf_gemm_desc {
+  int32_t dtype_ab;       /* XF_DT_BF16 (fp32 accumulate) or XF_DT_S8 (int32 accumulate) */
+  int32_t dtype_d;        /* XF_DT_BF16; XF_DT_F32 / XF_DT_S32 give the raw accumulator after the
+                             epilogue steps that are enabled (none => exact accumulator) */
+  int32_t M, N, K, L;
+  const void* A; int64_t lda; int64_t batch_a;
+  const void* B; int64_t ldb; int64_t batch_b;
+  void* D;       int64_t ldd; int64_t batch_d;
+  int32_t tile_m, tile_n, tile_k; /* the caller's TileShape: a hint, mapped to a native CTA tile */
+  int32_t flags;          /* XF_FLAG_* */
+  xf_epilogue_desc epi;
+} xf_gemm_desc;
+
+/* flags */
+#define XF_FLAG_DIRECT_STORE 1   /* write D with plain global stores instead of TMA stores */
+#define XF_FLAG_FORCE_1CTA   2   /* never pair CTAs (cta_group::1 only) */
+#define XF_FLAG_FORCE_2CTA   4   /* always pair CTAs (cta_group::2) when the shape allows */
+#define XF_FLAG_FORCE_BN128  8   /* use the 128-column CTA tile */
+#define XF_FLAG_FORCE_BN256  16  /* use the 256-column CTA tile */
+
+typedef struct xf_plan xf_plan;
+
+/* Checks a problem without touching the GPU.  Returns XF_SUCCESS or the reason it is refused. */
+XF_API xf_status xf_gemm_can_implement(const xf_gemm_desc* desc);
+/* Bytes of caller-owned workspace xf_gemm_plan_create needs (currently a 16-byte status word). */
+XF_API xf_status xf_gemm_workspace_size(const xf_gemm_desc* desc, size_t* bytes);
+/* Copies the descriptor, picks a kernel, encodes TMA tensor maps.  workspace may be NULL when
+ * xf_gemm_workspace_size reported 0; otherwise it must stay valid for the plan's lifetime. */
+XF_API xf_status xf_gemm_plan_create(const xf_gemm_desc* desc, void* workspace, xf_plan** plan);
+/* Enqueues one fused launch on `stream` (a cudaStream_t; NULL = default stream).  Re-entrant. */
+XF_API xf_status xf_gemm_run(xf_plan* plan, void* stream);
+/* Reads back (synchronously) the device status word of the plan's last launches:
+ * 0 = ok, otherwise the code of the bounded wait that gave up. */
+XF_API xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code);
+/* Name of the kernel variant the plan selected, e.g. "bf16_128x256_cta2_s6". */
+XF_API const char* xf_gemm_plan_kernel_name(const xf_plan* plan);
+XF_API xf_status xf_plan_destroy(xf_plan* plan);
+
+/* Thread-local text of the last error produced by any entry point on this thread. */
+XF_API const char* xf_last_error_string(void);
+XF_API const char* xf_status_string(xf_status s);
+/* Library version and the SM architecture the kernels were compiled for (100 => sm_100a). */
+XF_API int32_t xf_version(void);
+XF_API int32_t xf_compiled_arch(void);
+
+/*
+ * Stand-alone (unfused) elementwise passes over a bf16 [L][M][N] tensor, in place; these are the
+ * baseline the fused kernels are compared with (include/xe-fuse/standalone/ops.hpp).
+ */
+XF_API xf_status xf_sa_scale_rows(void* D, const float* scale, int M, int N, int L, void* stream);
+XF_API xf_status xf_sa_scale_cols(void* D, const float* scale, int M, int N, int L, void* stream);
+XF_API xf_status xf_sa_add_residual(void* D, const void* residual, int M, int N, int L, void* stream);
+XF_API xf_status xf_sa_residual_gamma(void* D, const void* residual, const float* gamma,
+                                      int M, int N, int L, void* stream);
+XF_API xf_status xf_sa_swiglu(void* D, int M, int N, int L, void* stream);
+XF_API xf_status xf_sa_geglu(void* D, int M, int N, int L, void* stream);
+/* out = rope(in); in and out are distinct buffers (ops.hpp:119-144). */
+XF_API xf_status xf_sa_rope(void* out, const void* in, const float* cos_sin, int M, int N, int L,
+                            void* stream);
+/* out = rope(in * scale[m]); in and out are distinct buffers (ops.hpp:146-176). */
+XF_API xf_status xf_sa_rope_scaled(void* out, const void* in, const float* scale,
+                                   const float* cos_sin, int M, int N, int L, void* stream);
+XF_API xf_status xf_sa_unary(void* D, int unary, int M, int N, int L, void* stream);
+XF_API xf_status xf_sa_bias_add(void* D, const float* bias, int M, int N, int L, void* stream);
+/* out_bf16 = float(acc_i32) * scale_token[m] * scale_channel[n] (ops.hpp:335-354). */
+XF_API xf_status xf_sa_dequant_w8a8(void* out, const int32_t* acc, const float* scale_token,
+                                    const float* scale_channel, int M, int N, int L, void* stream);
+/* rstd[m] = 1/sqrt(mean_n x[m,n]^2 + eps) over bf16 rows (compute_rstd.hpp:12-49). */
+XF_API xf_status xf_compute_rstd(const void* x, float* rstd, int M, int N, int L, float eps,
+                                 void* stream);
+/* RMS-normalise a bf16 row and quantise it to int8 with a per-token absmax scale that absorbs
+ * rstd (compute_rstd.hpp:67-125). */
+XF_API xf_status xf_compute_rstd_and_quantize(const void* x, int8_t* xq, float* scale_token,
+                                              int M, int N, int L, float eps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XEFUSE_B200_H_ */

@@ -1,0 +1,510 @@
+// Host side of the fused GEMM: argument checks, kernel/tile selection, TMA tensor-map encoding,
+// cluster launch.  Exposes the xf_gemm_* entry points declared in include/xefuse_b200.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/xefuse_b200.h"
+#include "xf_gemm_kernel.cuh"
+#include "xf_host_util.h"
+
+namespace xf {
+
+// ---------------------------------------------------------------------------- error text
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+const char* last_error() { return g_err; }
+
+// ---------------------------------------------------------------------------- driver entry
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+static bool encode_3d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t d0,
+                      uint64_t d1, uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes,
+                      uint32_t b0, uint32_t b1, CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (CUresult %d) dims={%llu,%llu,%llu} strides={%llu,%llu} box={%u,%u}",
+              (int)r, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2,
+              (unsigned long long)stride1_bytes, (unsigned long long)stride2_bytes, b0, b1);
+    return false;
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------- kernel table
+typedef void (*KernelFn)(const GemmParams);
+
+struct Variant {
+  int kind, bn, ctas, stages, smem;
+  KernelFn fn;
+  const char* name;
+};
+
+#define XF_VARIANT(KIND, BN, CTAS, NAME)                                             \
+  {KIND, BN, CTAS, TileCfg<KIND, BN, CTAS>::STAGES, TileCfg<KIND, BN, CTAS>::SMEM_BYTES, \
+   gemm_evt_kernel<KIND, BN, CTAS>, NAME}
+
+static const Variant g_variants[] = {
+    XF_VARIANT(0, 256, 2, "bf16_256x256_cta2"),
+    XF_VARIANT(0, 256, 1, "bf16_128x256_cta1"),
+    XF_VARIANT(0, 128, 2, "bf16_256x128_cta2"),
+    XF_VARIANT(0, 128, 1, "bf16_128x128_cta1"),
+    XF_VARIANT(1, 256, 2, "s8_256x256_cta2"),
+    XF_VARIANT(1, 256, 1, "s8_128x256_cta1"),
+    XF_VARIANT(1, 128, 1, "s8_128x128_cta1"),
+};
+static const int g_num_variants = sizeof(g_variants) / sizeof(g_variants[0]);
+
+}  // namespace xf
+
+struct xf_plan {
+  xf::GemmParams params;
+  const xf::Variant* variant;
+  int grid;
+  int device;
+  char name[64];
+};
+
+namespace xf {
+
+static int elem_size(int dt) {
+  switch (dt) {
+    case XF_DT_BF16: return 2;
+    case XF_DT_S8: return 1;
+    default: return 4;
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static xf_status check_vec(const xf_vec& v, const char* what) {
+  if (!v.enabled) return XF_SUCCESS;
+  if (v.dtype != XF_DT_F32 && v.dtype != XF_DT_BF16) {
+    set_error("%s: vector dtype must be f32 or bf16", what);
+    return XF_ERR_INVALID_DATA_TYPE;
+  }
+  return XF_SUCCESS;
+}
+
+static xf_status check_mat(const xf_mat& m, const char* what, int N, bool allow_bf16) {
+  if (!m.enabled) return XF_SUCCESS;
+  if (m.ptr == nullptr) {
+    set_error("%s: null pointer", what);
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  if (!(m.dtype == XF_DT_F32 || (allow_bf16 && m.dtype == XF_DT_BF16))) {
+    set_error("%s: unsupported dtype %d", what, m.dtype);
+    return XF_ERR_INVALID_DATA_TYPE;
+  }
+  if (m.ld < N) {
+    set_error("%s: row pitch %lld smaller than the %d columns read", what, (long long)m.ld, N);
+    return XF_ERR_INVALID_LAYOUT;
+  }
+  return XF_SUCCESS;
+}
+
+static xf_status validate(const xf_gemm_desc* d) {
+  if (!d) {
+    set_error("null descriptor");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  if (d->dtype_ab != XF_DT_BF16 && d->dtype_ab != XF_DT_S8) {
+    set_error("A/B dtype must be bf16 or int8 (got %d)", d->dtype_ab);
+    return XF_ERR_INVALID_DATA_TYPE;
+  }
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->L <= 0) {
+    set_error("problem extents must be positive (M=%d N=%d K=%d L=%d)", d->M, d->N, d->K, d->L);
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  if (!d->A || !d->B || !d->D) {
+    set_error("A, B and D must be non-null");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  const int es = elem_size(d->dtype_ab);
+  if (d->lda < d->K || d->ldb < d->N) {
+    set_error("leading dimensions too small (lda=%lld K=%d, ldb=%lld N=%d)", (long long)d->lda, d->K,
+              (long long)d->ldb, d->N);
+    return XF_ERR_INVALID_LAYOUT;
+  }
+  if (!aligned16(d->A) || !aligned16(d->B) || (d->lda * es) % 16 != 0 || (d->ldb * es) % 16 != 0 ||
+      (d->batch_a * es) % 16 != 0 || (d->batch_b * es) % 16 != 0) {
+    set_error("A/B base pointers, row pitches and batch strides must be multiples of 16 bytes "
+              "(lda=%lld ldb=%lld, %d-byte elements)", (long long)d->lda, (long long)d->ldb, es);
+    return XF_ERR_MISALIGNED_OPERAND;
+  }
+  const xf_epilogue_desc& e = d->epi;
+  const bool any_epi = e.residual.enabled || e.aux_store.enabled || e.row_scale.enabled ||
+                       e.col_scale.enabled || e.bias.enabled || e.unary != XF_UNARY_NONE ||
+                       e.pair != XF_PAIR_NONE;
+  if (d->dtype_d == XF_DT_S32) {
+    if (d->dtype_ab != XF_DT_S8 || any_epi) {
+      set_error("int32 output is the raw int8 accumulator: needs int8 inputs and an empty epilogue");
+      return XF_ERR_NOT_SUPPORTED;
+    }
+  } else if (d->dtype_d != XF_DT_BF16 && d->dtype_d != XF_DT_F32) {
+    set_error("D dtype must be bf16, f32 or s32 (got %d)", d->dtype_d);
+    return XF_ERR_INVALID_DATA_TYPE;
+  }
+  if (e.unary < XF_UNARY_NONE || e.unary > XF_UNARY_EXP || e.pair < XF_PAIR_NONE ||
+      e.pair > XF_PAIR_SWAP) {
+    set_error("unknown unary (%d) or pair (%d) op", e.unary, e.pair);
+    return XF_ERR_NOT_SUPPORTED;
+  }
+  if (e.pair != XF_PAIR_NONE && (d->N & 1)) {
+    set_error("pair ops need an even N (N=%d)", d->N);
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  const bool compact = e.out_layout == XF_OUT_COMPACT;
+  if (compact) {
+    if (e.pair != XF_PAIR_SWIGLU && e.pair != XF_PAIR_GEGLU) {
+      set_error("the compact [M,N/2] layout needs a SwiGLU/GeGLU pair op");
+      return XF_ERR_NOT_SUPPORTED;
+    }
+    if (d->dtype_d != XF_DT_BF16) {
+      set_error("the compact layout writes bf16 only");
+      return XF_ERR_NOT_SUPPORTED;
+    }
+  } else if (e.out_layout != XF_OUT_FULL) {
+    set_error("unknown output layout %d", e.out_layout);
+    return XF_ERR_NOT_SUPPORTED;
+  }
+  const int n_out = compact ? d->N / 2 : d->N;
+  if (d->ldd < n_out) {
+    set_error("ldd=%lld smaller than the %d output columns", (long long)d->ldd, n_out);
+    return XF_ERR_INVALID_LAYOUT;
+  }
+  xf_status s;
+  if ((s = check_vec(e.row_scale, "row_scale")) != XF_SUCCESS) return s;
+  if ((s = check_vec(e.col_scale, "col_scale")) != XF_SUCCESS) return s;
+  if ((s = check_vec(e.bias, "bias")) != XF_SUCCESS) return s;
+  if ((s = check_mat(e.residual, "residual", d->N, true)) != XF_SUCCESS) return s;
+  if (e.aux_store.enabled) {
+    if (!e.aux_store.ptr || e.aux_store.dtype != XF_DT_BF16 || e.aux_store.ld < d->N) {
+      set_error("aux_store must be a non-null bf16 [M,N] tensor");
+      return XF_ERR_NOT_SUPPORTED;
+    }
+  }
+  if (e.pair == XF_PAIR_ROPE) {
+    if (e.cos_sin_period < 0 || (e.cos_sin_period % 32) != 0) {
+      set_error("cos_sin_period must be 0 or a multiple of 32 (got %d)", e.cos_sin_period);
+      return XF_ERR_NOT_SUPPORTED;
+    }
+    xf_mat cs = e.cos_sin;
+    cs.enabled = 1;
+    const int width = e.cos_sin_period > 0 ? e.cos_sin_period : d->N;
+    if ((s = check_mat(cs, "cos_sin", width, false)) != XF_SUCCESS) return s;
+  }
+  return XF_SUCCESS;
+}
+
+static VecArg to_vec(const xf_vec& v) {
+  VecArg a;
+  a.ptr = v.ptr;
+  a.batch_stride = v.batch_stride;
+  a.null_default = v.null_default;
+  a.dtype = v.dtype;
+  a.enabled = v.enabled ? 1 : 0;
+  a.pad_ = 0;
+  return a;
+}
+static MatArg to_mat(const xf_mat& m) {
+  MatArg a;
+  a.ptr = m.ptr;
+  a.ld = m.ld;
+  a.batch_stride = m.batch_stride;
+  a.dtype = m.dtype;
+  a.enabled = m.enabled ? 1 : 0;
+  return a;
+}
+
+static int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Picks the CTA tile.  The caller's TileShape (an Intel Xe work-group tile) is only a hint; the
+// native tiles are {128,256} rows x {128,256} columns.  The estimate is waves x tile cost, with a
+// mild preference for the paired-CTA 256x256 tile, which halves shared-memory traffic for B.
+static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
+  const int kind = d->dtype_ab == XF_DT_BF16 ? 0 : 1;
+  const Variant* best = nullptr;
+  double best_cost = 0;
+  for (int i = 0; i < g_num_variants; ++i) {
+    const Variant& v = g_variants[i];
+    if (v.kind != kind) continue;
+    if ((d->flags & XF_FLAG_FORCE_1CTA) && v.ctas != 1) continue;
+    if ((d->flags & XF_FLAG_FORCE_2CTA) && v.ctas != 2) continue;
+    if ((d->flags & XF_FLAG_FORCE_BN128) && v.bn != 128) continue;
+    if ((d->flags & XF_FLAG_FORCE_BN256) && v.bn != 256) continue;
+    const int tiles = ceil_div(d->M, 128 * v.ctas) * ceil_div(d->N, v.bn) * d->L;
+    const int units = sm_count / v.ctas;
+    const int waves = ceil_div(tiles, units);
+    // relative time of one tile on its unit (lower is better per unit of work)
+    double eff = (v.bn == 256 ? 1.0 : 0.88) * (v.ctas == 2 ? 1.0 : 0.93);
+    double tile_work = 128.0 * v.bn;  // per SM
+    double cost = waves * tile_work / eff;
+    if (!best || cost < best_cost * 0.999) {
+      best = &v;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* plan) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    set_error("no CUDA device: %s", cudaGetErrorString(cudaGetLastError()));
+    return XF_ERR_ARCH_MISMATCH;
+  }
+  int major = 0, sm_count = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (major != 10) {
+    set_error("this library holds sm_100a code only; device %d has compute capability %d.x", dev, major);
+    return XF_ERR_ARCH_MISMATCH;
+  }
+  const Variant* v = select_variant(d, sm_count);
+  if (!v) {
+    set_error("no kernel variant matches the requested flags");
+    return XF_ERR_NOT_SUPPORTED;
+  }
+  plan->variant = v;
+  plan->device = dev;
+  GemmParams& p = plan->params;
+  memset(&p, 0, sizeof(p));
+  const int es = elem_size(d->dtype_ab);
+  const int kblk = 128 / es;
+  const int grp_cols = 128 / es;
+  p.M = d->M; p.N = d->N; p.K = d->K; p.L = d->L;
+  p.tiles_m = ceil_div(d->M, 128 * v->ctas);
+  p.tiles_n = ceil_div(d->N, v->bn);
+  p.num_kb = ceil_div(d->K, kblk);
+  p.group_m = (v->ctas == 2) ? 8 : 16;
+  p.a_batched = (d->L > 1 && d->batch_a != 0) ? 1 : 0;
+  p.b_batched = (d->L > 1 && d->batch_b != 0) ? 1 : 0;
+  p.D = d->D; p.ldd = d->ldd; p.batch_d = d->batch_d;
+  p.d_dtype = d->dtype_d;
+  p.status = reinterpret_cast<int*>(workspace);
+  p.wait_budget = 4000000000LL;  // about two seconds of SM clocks
+  const xf_epilogue_desc& e = d->epi;
+  p.epi.residual = to_mat(e.residual);
+  p.epi.aux_store = to_mat(e.aux_store);
+  p.epi.row_scale = to_vec(e.row_scale);
+  p.epi.col_scale = to_vec(e.col_scale);
+  p.epi.bias = to_vec(e.bias);
+  p.epi.cos_sin = to_mat(e.cos_sin);
+  p.epi.cos_sin.enabled = (e.pair == XF_PAIR_ROPE);
+  p.epi.cos_sin_period = e.cos_sin_period;
+  p.epi.unary = e.unary;
+  p.epi.pair = e.pair;
+  p.epi.compact = (e.out_layout == XF_OUT_COMPACT) ? 1 : 0;
+
+  const int n_out = p.epi.compact ? d->N / 2 : d->N;
+  const bool tma_store_ok = d->dtype_d == XF_DT_BF16 && aligned16(d->D) && (d->ldd * 2) % 16 == 0 &&
+                            (d->batch_d * 2) % 16 == 0 && !(d->flags & XF_FLAG_DIRECT_STORE);
+  p.direct_store = tma_store_ok ? 0 : 1;
+
+  const CUtensorMapDataType dt =
+      d->dtype_ab == XF_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const uint64_t la = p.a_batched ? d->L : 1, lb = p.b_batched ? d->L : 1;
+  const uint64_t sa2 = p.a_batched ? (uint64_t)d->batch_a * es : (uint64_t)d->lda * es * d->M;
+  const uint64_t sb2 = p.b_batched ? (uint64_t)d->batch_b * es : (uint64_t)d->ldb * es * d->K;
+  if (!encode_3d(&p.tm_a, dt, d->A, d->K, d->M, la, (uint64_t)d->lda * es, sa2, kblk, 128,
+                 CU_TENSOR_MAP_SWIZZLE_128B))
+    return XF_ERR_INTERNAL;
+  if (!encode_3d(&p.tm_b, dt, d->B, d->N, d->K, lb, (uint64_t)d->ldb * es, sb2, grp_cols, kblk,
+                 CU_TENSOR_MAP_SWIZZLE_128B))
+    return XF_ERR_INTERNAL;
+  if (!p.direct_store) {
+    const uint64_t sd2 = d->L > 1 ? (uint64_t)d->batch_d * 2 : (uint64_t)d->ldd * 2 * d->M;
+    if (!encode_3d(&p.tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d->D, n_out, d->M, d->L,
+                   (uint64_t)d->ldd * 2, sd2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+      return XF_ERR_INTERNAL;
+  }
+
+  cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(v->fn),
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem);
+  if (ce != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(smem=%d) failed: %s", v->smem, cudaGetErrorString(ce));
+    return XF_ERR_INTERNAL;
+  }
+  const int total_tiles = p.tiles_m * p.tiles_n * d->L;
+  int units = sm_count / v->ctas;
+  if (v->ctas == 2) {
+    // number of CTA pairs that can be co-resident (GPC boundaries may leave an SM unpaired)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count - (sm_count & 1), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = v->smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int nclusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&nclusters, reinterpret_cast<const void*>(v->fn), &cfg) ==
+            cudaSuccess && nclusters > 0)
+      units = nclusters;
+    else
+      cudaGetLastError();
+  }
+  const int nunits = total_tiles < units ? total_tiles : units;
+  plan->grid = nunits * v->ctas;
+  snprintf(plan->name, sizeof(plan->name), "%s_s%d", v->name, v->stages);
+  if (p.status) {
+    ce = cudaMemset(p.status, 0, 16);
+    if (ce != cudaSuccess) {
+      set_error("clearing the workspace status word failed: %s", cudaGetErrorString(ce));
+      return XF_ERR_INTERNAL;
+    }
+  }
+  return XF_SUCCESS;
+}
+
+}  // namespace xf
+
+extern "C" {
+
+xf_status xf_gemm_can_implement(const xf_gemm_desc* desc) { return xf::validate(desc); }
+
+xf_status xf_gemm_workspace_size(const xf_gemm_desc* desc, size_t* bytes) {
+  if (!bytes) {
+    xf::set_error("null output pointer");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  (void)desc;
+  *bytes = 16;
+  return XF_SUCCESS;
+}
+
+xf_status xf_gemm_plan_create(const xf_gemm_desc* desc, void* workspace, xf_plan** out) {
+  if (!out) {
+    xf::set_error("null plan output pointer");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  *out = nullptr;
+  xf_status s = xf::validate(desc);
+  if (s != XF_SUCCESS) return s;
+  xf_plan* plan = static_cast<xf_plan*>(calloc(1, sizeof(xf_plan) + 64));
+  if (!plan) {
+    xf::set_error("out of host memory");
+    return XF_ERR_MEMORY_ALLOCATION;
+  }
+  s = xf::build_plan(desc, workspace, plan);
+  if (s != XF_SUCCESS) {
+    free(plan);
+    return s;
+  }
+  *out = plan;
+  return XF_SUCCESS;
+}
+
+xf_status xf_gemm_run(xf_plan* plan, void* stream) {
+  if (!plan) {
+    xf::set_error("null plan");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan->grid, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = plan->variant->smem;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = plan->variant->ctas;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, plan->variant->fn, plan->params);
+  if (e != cudaSuccess) {
+    xf::set_error("launch of %s failed: %s", plan->name, cudaGetErrorString(e));
+    return XF_ERR_INTERNAL;
+  }
+  return XF_SUCCESS;
+}
+
+xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code) {
+  if (!plan || !device_code) {
+    xf::set_error("null argument");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  *device_code = 0;
+  if (!plan->params.status) return XF_SUCCESS;
+  cudaError_t e = cudaMemcpy(device_code, plan->params.status, sizeof(int32_t), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) {
+    xf::set_error("reading the status word failed: %s", cudaGetErrorString(e));
+    return XF_ERR_INTERNAL;
+  }
+  if (*device_code != 0) {
+    xf::set_error("kernel %s gave up in a bounded wait (device code %d)", plan->name, *device_code);
+    return XF_ERR_INTERNAL;
+  }
+  return XF_SUCCESS;
+}
+
+const char* xf_gemm_plan_kernel_name(const xf_plan* plan) { return plan ? plan->name : ""; }
+
+xf_status xf_plan_destroy(xf_plan* plan) {
+  free(plan);
+  return XF_SUCCESS;
+}
+
+const char* xf_last_error_string(void) { return xf::last_error(); }
+
+const char* xf_status_string(xf_status s) {
+  switch (s) {
+    case XF_SUCCESS: return "Success";
+    case XF_ERR_MISALIGNED_OPERAND: return "Error Misaligned Operand";
+    case XF_ERR_INVALID_DATA_TYPE: return "Error Invalid Data Type";
+    case XF_ERR_INVALID_LAYOUT: return "Error Invalid Layout";
+    case XF_ERR_INVALID_PROBLEM: return "Error Invalid Problem";
+    case XF_ERR_NOT_SUPPORTED: return "Error Not Supported";
+    case XF_ERR_WORKSPACE_NULL: return "Error Workspace Null";
+    case XF_ERR_INTERNAL: return "Error Internal";
+    case XF_ERR_ARCH_MISMATCH: return "Error Architecture Mismatch";
+    case XF_ERR_INSUFFICIENT_DRIVER: return "Error Insufficient Driver";
+    case XF_ERR_MEMORY_ALLOCATION: return "Error Memory Allocation failed";
+    default: return "Invalid status";
+  }
+}
+
+int32_t xf_version(void) { return 100; }
+int32_t xf_compiled_arch(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,575 @@
+// Persistent, warp-specialised fused GEMM + epilogue kernel for sm_100a.
+//
+//   D = epilogue(A[M,K] * B[K,N])      A row-major (K contiguous), B row-major (N contiguous)
+//
+// One CTA (CTAS == 1) or a pair of CTAs on neighbouring SMs (CTAS == 2, cta_group::2) owns a
+// (128*CTAS) x BN output tile.  Roles inside a 256-thread CTA:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A and B stages
+//   warp 1      MMA issuer:   one lane issues tcgen05.mma (kind::f16 / kind::i8) into TMEM
+//   warp 2      TMEM allocator
+//   warps 4-7   epilogue:     tcgen05.ld the accumulator (one row per thread, 32 columns per
+//               load), run the flat epilogue program in registers, stage bf16 rows in swizzled
+//               shared memory and TMA-store them
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
+// the main loop of tile i+1.  Adjacent output columns (2k, 2k+1) are adjacent registers of one
+// thread, so SwiGLU / GeGLU / RoPE need no cross-lane traffic.
+//
+// Shared memory per stage: A 128 rows x 128 B (K-major, 128-B swizzle) and B as BN/CTAS columns
+// split into 128-B column groups of KBLK rows each (MN-major, 128-B swizzle), exactly as the TMA
+// boxes land.  With CTAS == 2 each CTA loads its own 128 rows of A and its own half of the B
+// columns; no load is multicast.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "xf_params.h"
+#include "xf_ptx.cuh"
+
+namespace xf {
+
+template <int KIND, int BN_, int CTAS_>
+struct TileCfg {
+  static constexpr int BN = BN_;
+  static constexpr int CTAS = CTAS_;
+  static constexpr int BM = 128;                       // rows per CTA
+  static constexpr int ES = (KIND == 0) ? 2 : 1;       // bytes per A/B element
+  static constexpr int KBLK = 128 / ES;                // K elements per stage (128 B of K)
+  static constexpr int UK = 32 / ES;                   // K elements per tcgen05.mma
+  static constexpr int BN_CTA = BN / CTAS;             // B columns one CTA loads
+  static constexpr int GRP_COLS = 128 / ES;            // columns per 128-B group
+  static constexpr int NGRP = BN_CTA / GRP_COLS;       // column groups per CTA
+  static constexpr int GRP_BYTES = KBLK * 128;
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = NGRP * GRP_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BUF_BYTES = 2048;           // 32 rows x 64 B
+  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
+  static constexpr int VEC_BYTES = 4 * 2 * BN * 4;     // {col_scale, bias} per epilogue warp
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int SMEM_LIMIT = 227 * 1024;
+  static constexpr int STAGES_RAW =
+      (SMEM_LIMIT - 1024 - EPI_BYTES - VEC_BYTES - BAR_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM_BYTES =
+      1024 + STAGES * STAGE_BYTES + EPI_BYTES + VEC_BYTES + BAR_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;             // double-buffered accumulator
+  static_assert(NGRP >= 1, "B tile narrower than one 128-byte column group");
+  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512 || TMEM_COLS == 128, "TMEM columns");
+  static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
+};
+
+// tcgen05 instruction descriptor: D format, A/B formats, A K-major, B MN-major, N>>3, M>>4.
+template <int KIND, int BN, int CTAS>
+__host__ __device__ constexpr uint32_t make_idesc() {
+  uint32_t c_fmt = (KIND == 0) ? 1u : 2u;  // F32 : S32
+  uint32_t ab_fmt = 1u;                    // BF16 (kind::f16) : signed 8-bit (kind::i8)
+  return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (0u << 15) | (1u << 16) |
+         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>((128 * CTAS) >> 4) << 24);
+}
+
+struct TileCoord {
+  int tm, tn, l;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile) {
+  TileCoord c;
+  const int per_batch = p.tiles_m * p.tiles_n;
+  c.l = tile / per_batch;
+  const int r = tile - c.l * per_batch;
+  const int grp_tiles = p.group_m * p.tiles_n;
+  const int grp = r / grp_tiles;
+  const int first_m = grp * p.group_m;
+  const int gsz = min(p.group_m, p.tiles_m - first_m);
+  const int rr = r - grp * grp_tiles;
+  c.tn = rr / gsz;
+  c.tm = first_m + (rr - c.tn * gsz);
+  return c;
+}
+
+__device__ __forceinline__ float load_vec_elem(const VecArg& v, long long idx) {
+  if (v.ptr == nullptr) return v.null_default;
+  if (v.dtype == DT_BF16)
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(v.ptr)[idx]);
+  return reinterpret_cast<const float*>(v.ptr)[idx];
+}
+
+__device__ __forceinline__ float unary_apply(int op, float x) {
+  switch (op) {
+    case UN_GELU: return x * 0.5f * (1.0f + erff(x * 0.7071067811865475f));
+    case UN_GELU_TANH: {
+      const float k = 0.7978845608028654f;
+      float x3 = x * x * x;
+      return x * 0.5f * (1.0f + tanhf(k * (x + 0.044715f * x3)));
+    }
+    case UN_SILU: return __fdividef(x, 1.0f + __expf(-x));
+    case UN_RELU: return x > 0.0f ? x : 0.0f;
+    case UN_SIGMOID: return __fdividef(1.0f, 1.0f + __expf(-x));
+    case UN_EXP: return __expf(x);
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);  // .x = lo (low 16 bits), .y = hi
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Loads 32 consecutive elements of row `row` of a full [M,N] operand, starting at column col0,
+// as floats.  Columns >= ncols_total read as 0.
+__device__ __forceinline__ void load_mat_row32(const MatArg& m, int l, int row, int col0,
+                                               int ncols_total, float (&out)[32]) {
+  const long long off = static_cast<long long>(l) * m.batch_stride +
+                        static_cast<long long>(row) * m.ld + col0;
+  if (m.dtype == DT_BF16) {
+    const __nv_bfloat16* ptr = reinterpret_cast<const __nv_bfloat16*>(m.ptr) + off;
+    if (col0 + 32 <= ncols_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+      const uint4* p4 = reinterpret_cast<const uint4*>(ptr);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 u = __ldg(p4 + j);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          out[j * 8 + t * 2 + 0] = __uint_as_float(w[t] << 16);
+          out[j * 8 + t * 2 + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        out[i] = (col0 + i < ncols_total) ? __bfloat162float(ptr[i]) : 0.0f;
+    }
+  } else {
+    const float* ptr = reinterpret_cast<const float*>(m.ptr) + off;
+    if (col0 + 32 <= ncols_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+      const float4* p4 = reinterpret_cast<const float4*>(ptr);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 f = __ldg(p4 + j);
+        out[j * 4 + 0] = f.x; out[j * 4 + 1] = f.y; out[j * 4 + 2] = f.z; out[j * 4 + 3] = f.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = (col0 + i < ncols_total) ? ptr[i] : 0.0f;
+    }
+  }
+}
+
+// Stores `n` (<= 32) packed bf16 values (pk holds pairs) to row-major global memory.
+__device__ __forceinline__ void store_bf16_row(__nv_bfloat16* ptr, const uint32_t* pk, int nvalid,
+                                               int nfull) {
+  if (nvalid >= nfull && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+    uint4* p4 = reinterpret_cast<uint4*>(ptr);
+    for (int j = 0; j < nfull / 8; ++j)
+      p4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+  } else {
+    for (int i = 0; i < nfull; ++i) {
+      if (i < nvalid) {
+        uint32_t w = pk[i >> 1];
+        uint16_t h = (i & 1) ? static_cast<uint16_t>(w >> 16) : static_cast<uint16_t>(w & 0xFFFF);
+        reinterpret_cast<uint16_t*>(ptr)[i] = h;
+      }
+    }
+  }
+}
+
+// Runs the flat epilogue program on 32 accumulator columns of one row.
+//   r      raw TMEM words (fp32 bits or int32)
+//   v      results; for the compact layout only v[0..15] are meaningful (one per pair)
+//   gcol0  global column of r[0];  tcol0 column inside the CTA tile (index into cvec/bvec)
+template <int KIND>
+__device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const uint32_t (&r)[32],
+                                               float (&v)[32], int row, bool row_ok, int l,
+                                               int gcol0, int tcol0, float rs, const float* cvec,
+                                               const float* bvec) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    v[i] = (KIND == 0) ? __uint_as_float(r[i]) : static_cast<float>(static_cast<int>(r[i]));
+
+  if (e.residual.enabled && row_ok) {
+    float t[32];
+    load_mat_row32(e.residual, l, row, gcol0, N, t);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += t[i];
+  }
+  if (e.aux_store.enabled && row_ok) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+    __nv_bfloat16* ptr = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(e.aux_store.ptr)) +
+                         static_cast<long long>(l) * e.aux_store.batch_stride +
+                         static_cast<long long>(row) * e.aux_store.ld + gcol0;
+    store_bf16_row(ptr, pk, N - gcol0, 32);
+  }
+  if (e.row_scale.enabled) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= rs;
+  }
+  if (e.col_scale.enabled) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= cvec[tcol0 + i];
+  }
+  if (e.bias.enabled) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += bvec[tcol0 + i];
+  }
+  if (e.unary != UN_NONE) {
+    const int op = e.unary;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = unary_apply(op, v[i]);
+  }
+  if (e.pair == PAIR_SWIGLU || e.pair == PAIR_GEGLU) {
+    const bool ge = (e.pair == PAIR_GEGLU);
+    const bool compact = e.compact != 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float g = v[2 * j], u = v[2 * j + 1];
+      float a;
+      if (ge) a = g * 0.5f * (1.0f + erff(g * 0.7071067811865475f));
+      else a = __fdividef(g, 1.0f + __expf(-g));
+      const float o = a * u;
+      if (compact) {
+        v[j] = o;  // j <= 2j: never clobbers an unread input
+      } else {
+        v[2 * j] = o;
+        v[2 * j + 1] = o;
+      }
+    }
+  } else if (e.pair == PAIR_ROPE) {
+    float cs[32];
+    if (row_ok) {
+      const int ccol = e.cos_sin_period > 0 ? (gcol0 % e.cos_sin_period) : gcol0;
+      const int climit = e.cos_sin_period > 0 ? e.cos_sin_period : N;
+      load_mat_row32(e.cos_sin, l, row, ccol, climit, cs);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) cs[i] = 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float xe = v[2 * j], xo = v[2 * j + 1];
+      const float c = cs[2 * j], s = cs[2 * j + 1];
+      v[2 * j] = xe * c + xo * s;
+      v[2 * j + 1] = -xe * s + xo * c;
+    }
+  } else if (e.pair == PAIR_SWAP) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float t = v[2 * j];
+      v[2 * j] = v[2 * j + 1];
+      v[2 * j + 1] = t;
+    }
+  }
+}
+
+template <int KIND, int BN, int CTAS>
+__global__ void __launch_bounds__(256, 1)
+gemm_evt_kernel(const __grid_constant__ GemmParams p) {
+  using C = TileCfg<KIND, BN, CTAS>;
+  constexpr int STAGES = C::STAGES;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+  uint8_t* stage_base = smem;
+  uint8_t* epi_base = smem + STAGES * C::STAGE_BYTES;
+  float* vec_base = reinterpret_cast<float*>(epi_base + C::EPI_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(vec_base) + C::VEC_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]   TMA bytes landed (leader CTA's is used)
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]   MMAs reading the stage have finished
+  uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]        accumulator buffer complete
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]    accumulator buffer drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
+  const int cluster_idx = (CTAS == 2) ? static_cast<int>(ptx::cluster_id_x()) : blockIdx.x;
+  const int num_clusters = (CTAS == 2) ? static_cast<int>(ptx::num_clusters_x()) : gridDim.x;
+  const int total_tiles = p.tiles_m * p.tiles_n * p.L;
+  const long long budget = p.wait_budget;
+
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&p.tm_a);
+    ptx::prefetch_tmap(&p.tm_b);
+    if (!p.direct_store && p.d_dtype == DT_BF16) ptx::prefetch_tmap(&p.tm_d);
+  }
+  if (warp == 1 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&tfull_bar[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&tempty_bar[b]), 4 * CTAS);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc<CTAS>(ptx::smem_u32(tmem_slot), C::TMEM_COLS);
+    ptx::tmem_relinquish<CTAS>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if constexpr (CTAS == 2) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_idx; tile < total_tiles && ok; tile += num_clusters) {
+        const TileCoord tc = decode_tile(p, tile);
+        const int row0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
+        const int col0 = tc.tn * BN + static_cast<int>(cta_rank) * C::BN_CTA;
+        const int la = p.a_batched ? tc.l : 0;
+        const int lb = p.b_batched ? tc.l : 0;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, budget)) {
+            if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_PRODUCER_EMPTY);
+            ok = false;
+            break;
+          }
+          const uint32_t my_full = ptx::smem_u32(&full_bar[stage]);
+          const uint32_t full_addr = (CTAS == 2) ? ptx::mapa(my_full, 0) : my_full;
+          if (cta_rank == 0) ptx::mbar_arrive_expect_tx(my_full, C::STAGE_BYTES * CTAS);
+          uint8_t* sa = stage_base + stage * C::STAGE_BYTES;
+          uint8_t* sb = sa + C::A_BYTES;
+          ptx::tma_load_3d<CTAS>(ptx::smem_u32(sa), &p.tm_a, full_addr, kb * C::KBLK, row0, la);
+#pragma unroll
+          for (int g = 0; g < C::NGRP; ++g)
+            ptx::tma_load_3d<CTAS>(ptx::smem_u32(sb + g * C::GRP_BYTES), &p.tm_b, full_addr,
+                                   col0 + g * C::GRP_COLS, kb * C::KBLK, lb);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc<KIND, BN, CTAS>();
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_idx; tile < total_tiles && ok; tile += num_clusters, ++it) {
+        const int buf = it & 1;
+        if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1u, budget)) {
+          if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_MMA_TMEM_EMPTY);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, budget)) {
+            if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_MMA_FULL);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(stage_base + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+          const uint64_t adesc = ptx::make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = ptx::make_smem_desc_sw128(sb, C::GRP_BYTES, 1024);
+#pragma unroll
+          for (int k = 0; k < C::KBLK / C::UK; ++k) {
+            // A: +32 B along K inside the 128-B swizzled row; B: +UK rows of 128 B
+            ptx::umma<KIND, CTAS>(d_tmem, adesc + static_cast<uint64_t>(k * (32 >> 4)),
+                                  bdesc + static_cast<uint64_t>(k * ((C::UK * 128) >> 4)), idesc,
+                                  (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t eb = ptx::smem_u32(&empty_bar[stage]);
+          ptx::umma_commit<CTAS>(eb);
+          if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(eb, 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        const uint32_t tb = ptx::smem_u32(&tfull_bar[buf]);
+        ptx::umma_commit<CTAS>(tb);
+        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(tb, 1));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const EpiParams& e = p.epi;
+    uint8_t* stg = epi_base + q * (2 * C::EPI_BUF_BYTES);
+    int sidx = 0;
+    const bool compact = e.compact != 0;
+    const int n_out = compact ? (p.N >> 1) : p.N;
+    const uint32_t tempty_leader =
+        (CTAS == 2) ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0) : ptx::smem_u32(&tempty_bar[0]);
+    int it = 0;
+    for (int tile = cluster_idx; tile < total_tiles; tile += num_clusters, ++it) {
+      const TileCoord tc = decode_tile(p, tile);
+      const int buf = it & 1;
+      const int m0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
+      const int n0 = tc.tn * BN;
+      const int l = tc.l;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      // Per-column vectors of this tile, staged once per warp (no cross-warp synchronisation).
+      float* cvec = vec_base + q * (2 * BN);
+      float* bvec = cvec + BN;
+      if (e.col_scale.enabled || e.bias.enabled) {
+        __syncwarp();
+        for (int i = lane; i < BN; i += 32) {
+          const int n = n0 + i;
+          float cs = 1.0f, bs = 0.0f;
+          if (n < p.N) {
+            if (e.col_scale.enabled)
+              cs = load_vec_elem(e.col_scale, static_cast<long long>(l) * e.col_scale.batch_stride + n);
+            if (e.bias.enabled)
+              bs = load_vec_elem(e.bias, static_cast<long long>(l) * e.bias.batch_stride + n);
+          }
+          cvec[i] = cs;
+          bvec[i] = bs;
+        }
+        __syncwarp();
+      }
+      float rs = 1.0f;
+      if (e.row_scale.enabled && row_ok)
+        rs = load_vec_elem(e.row_scale, static_cast<long long>(l) * e.row_scale.batch_stride + row);
+
+      if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[buf]), (it >> 1) & 1, budget)) {
+        if (p.status && lane == 0) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_EPI_TMEM_FULL);
+        break;
+      }
+      ptx::tc_fence_after();
+
+      const uint32_t t_row = tmem_base + static_cast<uint32_t>(buf * BN) +
+                             (static_cast<uint32_t>(q * 32) << 16);
+      const int ncols_tile = min(BN, p.N - n0);           // valid accumulator columns
+      const bool warp_rows_ok = (m0 + q * 32) < p.M;      // any row of this warp inside M
+      const int acc_per_chunk = compact ? 64 : 32;
+      const int nchunks = (ncols_tile + acc_per_chunk - 1) / acc_per_chunk;
+
+      for (int c = 0; c < nchunks; ++c) {
+        uint32_t pk[16];
+        float v[32];
+        uint32_t r[32];
+        const int tcol0 = c * acc_per_chunk;
+        ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
+        ptx::tmem_ld_wait();
+        if (!compact && c == nchunks - 1) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
+        }
+        if (p.d_dtype == DT_S32) {
+          // raw int32 accumulator, no epilogue steps (checked on the host)
+          if (row_ok) {
+            int* dp = reinterpret_cast<int*>(p.D) + static_cast<long long>(l) * p.batch_d +
+                      static_cast<long long>(row) * p.ldd + n0 + tcol0;
+            const int nv = p.N - (n0 + tcol0);
+            if (nv >= 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<uint4*>(dp)[j] =
+                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < nv) dp[i] = static_cast<int>(r[i]);
+            }
+          }
+          continue;
+        }
+        epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, tcol0, rs, cvec, bvec);
+        if (p.d_dtype == DT_F32) {
+          if (row_ok) {
+            float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(l) * p.batch_d +
+                        static_cast<long long>(row) * p.ldd + n0 + tcol0;
+            const int nv = p.N - (n0 + tcol0);
+            if (nv >= 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<float4*>(dp)[j] =
+                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < nv) dp[i] = v[i];
+            }
+          }
+          continue;
+        }
+        // bf16 output: 32 output columns per chunk
+        int out_col0;
+        if (!compact) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+          out_col0 = n0 + tcol0;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+          // second half of the 64 accumulator columns
+          if (tcol0 + 32 < ncols_tile) {
+            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0 + 32), r);
+            ptx::tmem_ld_wait();
+          }
+          if (c == nchunks - 1) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
+          }
+          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0 + 32, tcol0 + 32, rs, cvec,
+                               bvec);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) pk[8 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+          out_col0 = (n0 + tcol0) >> 1;
+        }
+        if (p.direct_store) {
+          if (row_ok) {
+            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) +
+                                static_cast<long long>(l) * p.batch_d +
+                                static_cast<long long>(row) * p.ldd + out_col0;
+            store_bf16_row(dp, pk, n_out - out_col0, 32);
+          }
+        } else if (warp_rows_ok) {
+          if (lane == 0) ptx::tma_store_wait_read<1>();  // the buffer used two stores ago is free
+          __syncwarp();
+          uint8_t* sbuf = stg + sidx * C::EPI_BUF_BYTES;
+          const int sw = (lane >> 1) & 3;  // 64-B swizzle: 16-B chunk index ^= address bits [7,9)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(sbuf + lane * 64 + ((j ^ sw) << 4)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_3d(&p.tm_d, ptx::smem_u32(sbuf), out_col0, m0 + q * 32, l);
+            ptx::tma_store_commit();
+          }
+          sidx ^= 1;
+        }
+      }
+      if (nchunks == 0) {  // cannot happen for a scheduled tile, kept so the barrier protocol is total
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
+      }
+    }
+    if (lane == 0) ptx::tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if constexpr (CTAS == 2) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<CTAS>(tmem_base, C::TMEM_COLS);
+  }
+}
+
+}  // namespace xf

@@ -1,0 +1,70 @@
+// Kernel parameter block shared by the host planner and the device code.
+#pragma once
+
+#include <cuda.h>
+#include <stdint.h>
+
+namespace xf {
+
+enum : int { DT_BF16 = 0, DT_S8 = 1, DT_F32 = 2, DT_S32 = 3 };
+enum : int { UN_NONE = 0, UN_GELU, UN_GELU_TANH, UN_SILU, UN_RELU, UN_SIGMOID, UN_EXP };
+enum : int { PAIR_NONE = 0, PAIR_SWIGLU, PAIR_GEGLU, PAIR_ROPE, PAIR_SWAP };
+
+// Device status codes written by a bounded wait that gave up (0 = ok).
+enum : int {
+  DEV_OK = 0,
+  DEV_TIMEOUT_PRODUCER_EMPTY = 1,
+  DEV_TIMEOUT_MMA_FULL = 2,
+  DEV_TIMEOUT_MMA_TMEM_EMPTY = 3,
+  DEV_TIMEOUT_EPI_TMEM_FULL = 4,
+};
+
+struct VecArg {
+  const void* ptr;
+  long long batch_stride;
+  float null_default;
+  int dtype;    // DT_F32 / DT_BF16
+  int enabled;
+  int pad_;
+};
+
+struct MatArg {
+  const void* ptr;
+  long long ld;
+  long long batch_stride;
+  int dtype;    // DT_BF16 / DT_F32
+  int enabled;
+};
+
+struct EpiParams {
+  MatArg residual;
+  MatArg aux_store;
+  VecArg row_scale;
+  VecArg col_scale;
+  VecArg bias;
+  MatArg cos_sin;
+  int cos_sin_period;
+  int unary;
+  int pair;
+  int compact;  // 1: D holds one value per column pair, [M, N/2]
+};
+
+struct alignas(64) GemmParams {
+  CUtensorMap tm_a;   // [L][M][K], box {128 B of K, 128 rows}, 128-B swizzle
+  CUtensorMap tm_b;   // [L][K][N], box {128 B of N, KBLK rows}, 128-B swizzle
+  CUtensorMap tm_d;   // [L][M][Nout] bf16, box {32 cols, 32 rows}, 64-B swizzle
+  int M, N, K, L;
+  int tiles_m, tiles_n;    // in units of the cluster tile (128*CTAS rows x BN columns)
+  int num_kb;              // ceil(K / KBLK)
+  int group_m;             // rasterisation group height in cluster tiles
+  int a_batched, b_batched;  // 0: batch stride 0, always use batch coordinate 0
+  void* D;
+  long long ldd, batch_d;
+  int d_dtype;             // DT_BF16 / DT_F32 / DT_S32
+  int direct_store;        // 1: plain global stores for D
+  int* status;             // device status word (may be null)
+  long long wait_budget;   // clock64 cycles a wait may take before giving up
+  EpiParams epi;
+};
+
+}  // namespace xf

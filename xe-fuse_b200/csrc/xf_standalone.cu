@@ -1,0 +1,441 @@
+// Stand-alone (unfused) elementwise passes over bf16 [L][M][N] tensors and the row-reduction
+// producers (rstd, activation quantisation).  These are HBM-bound: each thread moves 16-byte
+// vectors, grids are sized in whole waves of the SM count, and every kernel reads each input once.
+// They exist as the "unfused" arm the fused GEMM epilogues are measured against and as the
+// producers of the per-row vectors the fused kernels consume.
+//
+// Semantics follow include/xe-fuse/standalone/ops.hpp and include/xe-fuse/kernels/compute_rstd.hpp
+// of the reference: fp32 math on bf16 data, one round-to-nearest-even back to bf16.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/xefuse_b200.h"
+#include "xf_host_util.h"
+#include "xf_params.h"
+
+namespace xf {
+namespace sa {
+
+enum Op : int {
+  OP_SCALE_ROWS, OP_SCALE_COLS, OP_ADD_RESIDUAL, OP_RESIDUAL_GAMMA, OP_SWIGLU, OP_GEGLU, OP_ROPE,
+  OP_ROPE_SCALED, OP_UNARY, OP_BIAS_ADD, OP_DEQUANT
+};
+
+struct Args {
+  void* out;            // bf16 [L*M, N]
+  const void* in;       // bf16 source (== out for in-place ops) or int32 accumulator (dequant)
+  const void* mat;      // bf16 residual
+  const float* rowv;    // per-row vector, indexed by global row (batch*M + m)
+  const float* colv;    // per-column vector
+  const float* cos_sin; // fp32 [L*M, N]
+  long long rows;       // L*M
+  int M, N;
+  int unary;
+  int colv_batched;     // 1: colv index is batch*N + col
+};
+
+__device__ __forceinline__ float act(int op, float x) {
+  switch (op) {
+    case UN_GELU: return x * 0.5f * (1.0f + erff(x * 0.7071067811865475f));
+    case UN_GELU_TANH: {
+      float x3 = x * x * x;
+      return x * 0.5f * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x3)));
+    }
+    case UN_SILU: return x / (1.0f + __expf(-x));
+    case UN_RELU: return x > 0.0f ? x : 0.0f;
+    case UN_SIGMOID: return 1.0f / (1.0f + __expf(-x));
+    case UN_EXP: return __expf(x);
+    default: return x;
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&v)[VEC]) {
+  if constexpr (VEC == 8) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      v[2 * t] = __uint_as_float(w[t] << 16);
+      v[2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = __bfloat162float(p[i]);
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
+      w[t] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) p[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_f32(const float* p, float (&v)[VEC]) {
+  if constexpr (VEC == 8) {
+    float4 a = *reinterpret_cast<const float4*>(p);
+    float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = p[i];
+  }
+}
+
+// One thread owns VEC consecutive columns of one row; VEC divides N so a vector never straddles
+// rows.  Grid-stride loop over all vectors.
+template <int OP, int VEC>
+__global__ void __launch_bounds__(256) elementwise_kernel(const Args a) {
+  const long long vec_per_row = a.N / VEC;
+  const long long total = a.rows * vec_per_row;
+  for (long long idx = blockIdx.x * 256LL + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * 256LL) {
+    const long long row = idx / vec_per_row;
+    const int col = static_cast<int>(idx - row * vec_per_row) * VEC;
+    const long long off = row * a.N + col;
+    float v[VEC];
+    if constexpr (OP == OP_DEQUANT) {
+      const int* ip = reinterpret_cast<const int*>(a.in) + off;
+      if constexpr (VEC == 8) {
+        const int4 lo = *reinterpret_cast<const int4*>(ip);
+        const int4 hi = *reinterpret_cast<const int4*>(ip + 4);
+        v[0] = static_cast<float>(lo.x); v[1] = static_cast<float>(lo.y);
+        v[2] = static_cast<float>(lo.z); v[3] = static_cast<float>(lo.w);
+        v[4] = static_cast<float>(hi.x); v[5] = static_cast<float>(hi.y);
+        v[6] = static_cast<float>(hi.z); v[7] = static_cast<float>(hi.w);
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = static_cast<float>(ip[i]);
+      }
+    } else {
+      load_bf16<VEC>(reinterpret_cast<const __nv_bfloat16*>(a.in) + off, v);
+    }
+    const int batch = static_cast<int>(row / a.M);
+    if constexpr (OP == OP_SCALE_ROWS) {
+      const float s = a.rowv[row];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] *= s;
+    } else if constexpr (OP == OP_SCALE_COLS) {
+      float g[VEC];
+      load_f32<VEC>(a.colv + col, g);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] *= g[i];
+    } else if constexpr (OP == OP_ADD_RESIDUAL || OP == OP_RESIDUAL_GAMMA) {
+      float r[VEC];
+      load_bf16<VEC>(reinterpret_cast<const __nv_bfloat16*>(a.mat) + off, r);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] += r[i];
+      if constexpr (OP == OP_RESIDUAL_GAMMA) {
+        float g[VEC];
+        load_f32<VEC>(a.colv + col, g);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] *= g[i];
+      }
+    } else if constexpr (OP == OP_SWIGLU || OP == OP_GEGLU) {
+#pragma unroll
+      for (int j = 0; j < VEC / 2; ++j) {
+        const float g = v[2 * j], u = v[2 * j + 1];
+        const float o = (OP == OP_SWIGLU ? g / (1.0f + __expf(-g))
+                                         : g * 0.5f * (1.0f + erff(g * 0.7071067811865475f))) * u;
+        v[2 * j] = o;
+        v[2 * j + 1] = o;
+      }
+    } else if constexpr (OP == OP_ROPE || OP == OP_ROPE_SCALED) {
+      float cs[VEC];
+      load_f32<VEC>(a.cos_sin + off, cs);
+      float s = 1.0f;
+      if constexpr (OP == OP_ROPE_SCALED) s = a.rowv[row];
+#pragma unroll
+      for (int j = 0; j < VEC / 2; ++j) {
+        const float xe = v[2 * j] * s, xo = v[2 * j + 1] * s;
+        v[2 * j] = xe * cs[2 * j] + xo * cs[2 * j + 1];
+        v[2 * j + 1] = -xe * cs[2 * j + 1] + xo * cs[2 * j];
+      }
+    } else if constexpr (OP == OP_UNARY) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = act(a.unary, v[i]);
+    } else if constexpr (OP == OP_BIAS_ADD) {
+      float b[VEC];
+      load_f32<VEC>(a.colv + col, b);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] += b[i];
+    } else if constexpr (OP == OP_DEQUANT) {
+      const float st = a.rowv[row];
+      float sc[VEC];
+      load_f32<VEC>(a.colv + static_cast<long long>(batch) * a.N + col, sc);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = v[i] * st * sc[i];
+    }
+    store_bf16<VEC>(reinterpret_cast<__nv_bfloat16*>(a.out) + off, v);
+  }
+}
+
+static bool al16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int wave_grid(long long work_items) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long long blocks = (work_items + 255) / 256;
+  long long cap = static_cast<long long>(sms) * 16;  // 16 resident 256-thread blocks fill an SM's 64 warps twice over
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+template <int OP>
+static xf_status launch(const Args& a, bool pairwise, cudaStream_t st) {
+  if (a.rows <= 0 || a.N <= 0 || a.M <= 0) {
+    set_error("standalone op: extents must be positive");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  if (!a.out || !a.in) {
+    set_error("standalone op: null tensor pointer");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  const bool v8 = (a.N % 8 == 0) && al16(a.out) && al16(a.in) && al16(a.mat) && al16(a.colv) &&
+                  al16(a.cos_sin);
+  if (v8) {
+    const long long total = a.rows * (a.N / 8);
+    elementwise_kernel<OP, 8><<<wave_grid(total), 256, 0, st>>>(a);
+  } else if (a.N % 2 == 0) {
+    const long long total = a.rows * (a.N / 2);
+    elementwise_kernel<OP, 2><<<wave_grid(total), 256, 0, st>>>(a);
+  } else {
+    if (pairwise) {
+      set_error("standalone pair op needs an even N (N=%d)", a.N);
+      return XF_ERR_INVALID_PROBLEM;
+    }
+    const long long total = a.rows * a.N;
+    elementwise_kernel<OP, 1><<<wave_grid(total), 256, 0, st>>>(a);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("standalone kernel launch failed: %s", cudaGetErrorString(e));
+    return XF_ERR_INTERNAL;
+  }
+  return XF_SUCCESS;
+}
+
+// ------------------------------------------------------------------------ row reductions
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <bool IS_MAX>
+__device__ __forceinline__ float block_reduce(float v, float* red) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float r = (l < nw) ? red[l] : (IS_MAX ? 0.0f : 0.0f);
+  r = IS_MAX ? warp_max(r) : warp_sum(r);
+  return r;
+}
+
+// One 256-thread block per row; QUANT additionally writes the int8 row and its scale.
+template <bool QUANT>
+__global__ void __launch_bounds__(256) rstd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                   float* __restrict__ rstd_or_scale,
+                                                   int8_t* __restrict__ xq, long long rows, int N,
+                                                   float eps) {
+  __shared__ float red[8];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + row * N;
+    const bool vec = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
+    float ss = 0.0f;
+    if (vec) {
+      for (int c = threadIdx.x * 8; c < N; c += 256 * 8) {
+        float v[8];
+        load_bf16<8>(xr + c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+      }
+    } else {
+      for (int c = threadIdx.x; c < N; c += 256) {
+        float v = __bfloat162float(xr[c]);
+        ss += v * v;
+      }
+    }
+    ss = block_reduce<false>(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
+    if constexpr (!QUANT) {
+      if (threadIdx.x == 0) rstd_or_scale[row] = rstd;
+    } else {
+      float mx = 0.0f;
+      for (int c = threadIdx.x; c < N; c += 256)
+        mx = fmaxf(mx, fabsf(__bfloat162float(xr[c]) * rstd));
+      mx = block_reduce<true>(mx, red);
+      const float scale = mx / 127.0f + 1e-8f;
+      int8_t* qr = xq + row * N;
+      for (int c = threadIdx.x; c < N; c += 256) {
+        float q = roundf(__bfloat162float(xr[c]) * rstd / scale);  // half away from zero
+        q = fminf(fmaxf(q, -128.0f), 127.0f);
+        qr[c] = static_cast<int8_t>(q);
+      }
+      if (threadIdx.x == 0) rstd_or_scale[row] = scale;
+    }
+  }
+}
+
+}  // namespace sa
+}  // namespace xf
+
+using xf::sa::Args;
+using namespace xf::sa;
+
+static Args mk(void* out, const void* in, int M, int N, int L) {
+  Args a = {};
+  a.out = out;
+  a.in = in;
+  a.rows = static_cast<long long>(M) * L;
+  a.M = M;
+  a.N = N;
+  return a;
+}
+
+extern "C" {
+
+xf_status xf_sa_scale_rows(void* D, const float* scale, int M, int N, int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  a.rowv = scale;
+  if (!scale) { xf::set_error("scale_rows: null scale"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_SCALE_ROWS>(a, false, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_scale_cols(void* D, const float* scale, int M, int N, int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  a.colv = scale;
+  if (!scale) { xf::set_error("scale_cols: null scale"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_SCALE_COLS>(a, false, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_add_residual(void* D, const void* residual, int M, int N, int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  a.mat = residual;
+  if (!residual) { xf::set_error("add_residual: null residual"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_ADD_RESIDUAL>(a, false, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_residual_gamma(void* D, const void* residual, const float* gamma, int M, int N,
+                               int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  a.mat = residual;
+  a.colv = gamma;
+  if (!residual || !gamma) { xf::set_error("residual_gamma: null operand"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_RESIDUAL_GAMMA>(a, false, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_swiglu(void* D, int M, int N, int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  return launch<OP_SWIGLU>(a, true, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_geglu(void* D, int M, int N, int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  return launch<OP_GEGLU>(a, true, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_rope(void* out, const void* in, const float* cos_sin, int M, int N, int L,
+                     void* stream) {
+  Args a = mk(out, in, M, N, L);
+  a.cos_sin = cos_sin;
+  if (!cos_sin) { xf::set_error("rope: null cos_sin"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_ROPE>(a, true, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_rope_scaled(void* out, const void* in, const float* scale, const float* cos_sin,
+                            int M, int N, int L, void* stream) {
+  Args a = mk(out, in, M, N, L);
+  a.rowv = scale;
+  a.cos_sin = cos_sin;
+  if (!scale || !cos_sin) { xf::set_error("rope_scaled: null operand"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_ROPE_SCALED>(a, true, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_unary(void* D, int unary, int M, int N, int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  a.unary = unary;
+  if (unary < XF_UNARY_NONE || unary > XF_UNARY_EXP) {
+    xf::set_error("unary: unknown op %d", unary);
+    return XF_ERR_NOT_SUPPORTED;
+  }
+  return launch<OP_UNARY>(a, false, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_bias_add(void* D, const float* bias, int M, int N, int L, void* stream) {
+  Args a = mk(D, D, M, N, L);
+  a.colv = bias;
+  if (!bias) { xf::set_error("bias_add: null bias"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_BIAS_ADD>(a, false, static_cast<cudaStream_t>(stream));
+}
+
+xf_status xf_sa_dequant_w8a8(void* out, const int32_t* acc, const float* scale_token,
+                             const float* scale_channel, int M, int N, int L, void* stream) {
+  Args a = mk(out, acc, M, N, L);
+  a.rowv = scale_token;
+  a.colv = scale_channel;
+  if (!scale_token || !scale_channel) { xf::set_error("dequant_w8a8: null scale"); return XF_ERR_INVALID_PROBLEM; }
+  return launch<OP_DEQUANT>(a, false, static_cast<cudaStream_t>(stream));
+}
+
+static xf_status launch_rstd(const void* x, float* out, int8_t* xq, int M, int N, int L, float eps,
+                             void* stream) {
+  if (!x || !out || M <= 0 || N <= 0 || L <= 0) {
+    xf::set_error("compute_rstd: bad arguments");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  const long long rows = static_cast<long long>(M) * L;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long long grid = rows < static_cast<long long>(sms) * 8 ? rows : static_cast<long long>(sms) * 8;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (xq)
+    xf::sa::rstd_kernel<true><<<static_cast<int>(grid), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), out, xq, rows, N, eps);
+  else
+    xf::sa::rstd_kernel<false><<<static_cast<int>(grid), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), out, nullptr, rows, N, eps);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    xf::set_error("compute_rstd launch failed: %s", cudaGetErrorString(e));
+    return XF_ERR_INTERNAL;
+  }
+  return XF_SUCCESS;
+}
+
+xf_status xf_compute_rstd(const void* x, float* rstd, int M, int N, int L, float eps, void* stream) {
+  return launch_rstd(x, rstd, nullptr, M, N, L, eps, stream);
+}
+
+xf_status xf_compute_rstd_and_quantize(const void* x, int8_t* xq, float* scale_token, int M, int N,
+                                       int L, float eps, void* stream) {
+  if (!xq) {
+    xf::set_error("compute_rstd_and_quantize: null int8 output");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  return launch_rstd(x, scale_token, xq, M, N, L, eps, stream);
+}
+
+}  // extern "C"
