@@ -1,0 +1,538 @@
+#!/usr/bin/env python
+"""Benchmark of the fused GEMM + epilogue path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload k2] [--impl reference]
+
+A step is one pass of the hot path over one batch of synthetic input: one fused launch (the
+`pipeline` workload: its four launches).  Default workload: k2 = GEMM + RMSNorm row-scale + SwiGLU
+at the Llama-3-8B FFN gate/up shape (M=4096 tokens, K=4096, N=28672 interleaved gate/up columns,
+output [4096,14336] bf16).  With N GPUs the weight columns are sharded N-ways (activations and
+per-row scales replicated, nothing exchanged inside a stage), so total work is fixed: strong
+scaling.  Prints ONE JSON line on rank 0.
+
+  value     whole-job TFLOP/s (2*M*N*K per GEMM), inputs resident in HBM, CUDA-event timed,
+            max over ranks
+  e2e       the same metric through the C ABI with HOST buffers: every step copies the step's
+            activations + row scales host->device from pinned memory and the output device->host
+  roofline  tensor-core bound: achieved 2MNK / average launch time against the measured bf16 peak
+  cpu_baseline / --impl reference
+            the CPU oracle (a port of the reference's formulas; the reference has no CPU or CUDA
+            implementation of its own) timed on the host cores on a bounded row-sample
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "fused GEMM+epilogue TFLOP/s"
+
+# name -> list of stages: (preset, M, N, K, dtype)
+WORKLOADS = {
+    "k1": [("k1", 512, 4096, 4096, "bf16")],
+    "k2": [("k2", 4096, 28672, 4096, "bf16")],
+    "k4v2_q": [("k4v2", 4096, 4096, 4096, "bf16")],
+    "k4v2_kv": [("k4v2", 4096, 1024, 4096, "bf16")],
+    "w8a8": [("w8a8", 8192, 8192, 28672, "s8")],
+    # Llama-3-70B decoder-layer GEMM chain, M = 8192 tokens
+    "pipeline": [("k4v2", 8192, 10240, 8192, "bf16"), ("k0a", 8192, 8192, 8192, "bf16"),
+                 ("k2", 8192, 57344, 8192, "bf16"), ("k0a", 8192, 8192, 28672, "bf16")],
+}
+DESCR = {
+    "k1": "k1 GEMM+RMSNorm row-scale M=512 N=4096 K=4096 bf16",
+    "k2": "k2 GEMM+RMSNorm+SwiGLU Llama-3-8B FFN gate/up M=4096 K=4096 N=28672 (interleaved) -> [4096,14336] bf16",
+    "k4v2_q": "k4v2 GEMM+RMSNorm+RoPE Llama-3-8B Q-proj M=4096 K=4096 N=4096, table [4096,128] theta=5e5",
+    "k4v2_kv": "k4v2 GEMM+RMSNorm+RoPE Llama-3-8B K-proj M=4096 K=4096 N=1024, table [4096,128] theta=5e5",
+    "w8a8": "w8a8_dequant_biased Llama-3-70B FFN down M=8192 K=28672 N=8192 int8 -> bf16, bf16 bias",
+    "pipeline": "Llama-3-70B layer GEMM chain M=8192: QKV k4v2 (K=8192,N=10240), O k0a (8192,8192), "
+                "gate/up k2 (K=8192,N=57344), down k0a (K=28672,N=8192)",
+}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"bf16": d["bf16_tflops"], "bf16_sustained": d.get("bf16_tflops_sustained"),
+                "hbm": d["hbm_gbs"], "src": "measured"}
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "src": "fallback"}
+
+
+# ------------------------------------------------------------------------------ clocks sampler
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons of one GPU while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.uuid = uuid
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", self.uuid], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0=None, t1=None):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        for ts, l in self.lines:
+            if t0 is not None and not (t0 - 0.05 <= ts <= t1 + 0.1):
+                continue
+            f = [x.strip() for x in l.split(",")]
+            if len(f) >= 6 and f[0].isdigit():
+                rows.append(f)
+        if not rows:
+            rows = [[x.strip() for x in l.split(",")] for _, l in self.lines
+                    if l and l.split(",")[0].strip().isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons,
+                "samples": len(rows)}
+
+
+# ------------------------------------------------------------------------------ synthetic inputs
+def gen_stage_host(stage, rank, world, seed):
+    """Seeded host tensors of one stage for this rank's column shard (pinned where copied per step)."""
+    import torch
+    preset, M, N, K, dt = stage
+    assert N % world == 0
+    Ns = N // world
+    g = torch.Generator().manual_seed(seed)
+    gw = torch.Generator().manual_seed(seed * 7919 + 13 * rank + 1)   # per-shard weight stream
+    h = {}
+    if dt == "bf16":
+        X = torch.randn(M, K, generator=g, dtype=torch.float32)
+        h["R"] = torch.rsqrt((X * X).mean(dim=1) + 1e-6).contiguous()    # fp32 on the host
+        h["X"] = X.to(torch.bfloat16)
+        W = torch.empty(K, Ns, dtype=torch.bfloat16)
+        for k0 in range(0, K, 4096):                                      # bounded temporaries
+            k1 = min(K, k0 + 4096)
+            W[k0:k1] = (torch.randn(k1 - k0, Ns, generator=gw) * K ** -0.5).to(torch.bfloat16)
+        h["W"] = W
+    else:
+        X = torch.randn(M, K, generator=g, dtype=torch.float32).to(torch.bfloat16).float()
+        st = X.abs().amax(dim=1) / 127.0 + 1e-8                          # per-token absmax
+        h["X"] = torch.clamp(torch.round(X / st[:, None]), -128, 127).to(torch.int8)
+        h["R"] = st.contiguous()
+        W = torch.empty(K, Ns, dtype=torch.int8)
+        sc = torch.zeros(Ns)
+        Wf = torch.empty(K, Ns, dtype=torch.bfloat16)
+        for k0 in range(0, K, 4096):
+            k1 = min(K, k0 + 4096)
+            Wf[k0:k1] = (torch.randn(k1 - k0, Ns, generator=gw) * K ** -0.5).to(torch.bfloat16)
+        sc = Wf.float().abs().amax(dim=0) / 127.0 + 1e-8                  # per-channel absmax
+        for k0 in range(0, K, 4096):
+            k1 = min(K, k0 + 4096)
+            W[k0:k1] = torch.clamp(torch.round(Wf[k0:k1].float() / sc[None, :]), -128, 127).to(torch.int8)
+        h["W"] = W
+        h["sc"] = sc.contiguous()
+        h["bias"] = (torch.randn(Ns, generator=gw) * 0.02).to(torch.bfloat16)
+    if preset == "k0a":
+        h["residual"] = torch.randn(M, Ns, generator=gw).to(torch.bfloat16)
+        h["gamma"] = (1.0 + 0.02 * torch.randn(Ns, generator=gw)).contiguous()
+    if preset == "k4v2":
+        pos = torch.arange(M, dtype=torch.float32)[:, None]
+        i = torch.arange(64, dtype=torch.float32)[None, :]
+        ang = pos * torch.pow(torch.tensor(500000.0), -2.0 * i / 128.0)
+        cs = torch.empty(M, 128)
+        cs[:, 0::2] = torch.cos(ang)
+        cs[:, 1::2] = torch.sin(ang)
+        h["cos_sin"] = cs.contiguous()
+    h["X"] = h["X"].contiguous().pin_memory() if torch.cuda.is_available() else h["X"].contiguous()
+    h["R"] = h["R"].pin_memory() if torch.cuda.is_available() else h["R"]
+    return h
+
+
+def build_stage_gpu(capi, stage, h, dev):
+    """Device buffers + the fused plan (and the unfused baseline's pieces) of one stage."""
+    import torch
+    preset, M, N, K, dt = stage
+    Ns = h["W"].shape[1]
+    s = {"stage": stage, "Ns": Ns}
+    s["X"] = h["X"].to(dev, non_blocking=True)
+    s["R"] = h["R"].to(dev, non_blocking=True)
+    s["W"] = h["W"].to(dev)
+    kw = {}
+    n_out = Ns
+    if preset == "k1":
+        kw = dict(row_scale=s["R"])
+    elif preset == "k2":
+        kw = dict(row_scale=s["R"], pair="swiglu", compact=True)
+        n_out = Ns // 2
+    elif preset == "k4v2":
+        s["cos_sin"] = h["cos_sin"].to(dev)
+        kw = dict(row_scale=s["R"], pair="rope", cos_sin=s["cos_sin"], cos_sin_period=128)
+    elif preset == "k0a":
+        s["residual"] = h["residual"].to(dev)
+        s["gamma"] = h["gamma"].to(dev)
+        kw = dict(residual=s["residual"], col_scale=s["gamma"])
+    elif preset == "w8a8":
+        s["sc"] = h["sc"].to(dev)
+        s["bias"] = h["bias"].to(dev)
+        kw = dict(row_scale=s["R"], col_scale=s["sc"], bias=s["bias"])
+    s["D"] = torch.empty(M, n_out, dtype=torch.bfloat16, device=dev)
+    s["plan"] = capi.GemmPlan(s["X"], s["W"], s["D"], **kw)
+    s["flops"] = 2.0 * M * Ns * K
+    s["h2d_bytes"] = h["X"].numel() * h["X"].element_size() + h["R"].numel() * 4
+    s["d2h_bytes"] = s["D"].numel() * 2
+    s["bytes_resident"] = (s["X"].numel() * s["X"].element_size() + s["W"].numel() * s["W"].element_size()
+                           + s["D"].numel() * 2)
+    return s
+
+
+def build_unfused(capi, s, dev):
+    """Bare GEMM (identity epilogue) + the stand-alone kernel(s) the reference's unfused arm runs
+    (autotune/pipeline_template.cpp.j2:771-797)."""
+    import torch
+    preset, M, N, K, dt = s["stage"]
+    Ns = s["Ns"]
+    u = {}
+    if dt == "s8":
+        u["acc"] = torch.empty(M, Ns, dtype=torch.int32, device=dev)
+        u["out"] = torch.empty(M, Ns, dtype=torch.bfloat16, device=dev)
+        u["plan"] = capi.GemmPlan(s["X"], s["W"], u["acc"])
+        bias_f32 = s["bias"].float()
+        u["post"] = lambda: (capi.sa_dequant_w8a8(u["out"], u["acc"], s["R"], s["sc"]),
+                             capi.sa_bias_add(u["out"], bias_f32))
+        u["launches"] = 3
+    else:
+        u["out"] = torch.empty(M, Ns, dtype=torch.bfloat16, device=dev)
+        u["plan"] = capi.GemmPlan(s["X"], s["W"], u["out"])
+        if preset == "k1":
+            u["post"] = lambda: capi.sa_scale_rows(u["out"], s["R"])
+            u["launches"] = 2
+        elif preset == "k2":
+            u["post"] = lambda: (capi.sa_scale_rows(u["out"], s["R"]), capi.sa_swiglu(u["out"]))
+            u["launches"] = 3
+        elif preset == "k4v2":
+            u["tmp"] = torch.empty_like(u["out"])
+            u["cs_full"] = s["cos_sin"].repeat(1, Ns // 128).contiguous()
+            u["post"] = lambda: (u["tmp"].copy_(u["out"]),
+                                 capi.sa_rope_scaled(u["out"], u["tmp"], s["R"], u["cs_full"]))
+            u["launches"] = 3
+        elif preset == "k0a":
+            u["post"] = lambda: capi.sa_residual_gamma(u["out"], s["residual"], s["gamma"])
+            u["launches"] = 2
+    return u
+
+
+def time_loop(torch, fn, steps, flush=None):
+    """CUDA-event time of `steps` calls on the current stream, in ms.  With `flush`, a buffer larger
+    than L2 is overwritten before every step and only the steps are timed."""
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+    evs = []
+    for _ in range(steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs)
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_sample(stages, seconds_target, seed):
+    """Times the oracle on a row-sample of the workload; returns (tflops, rows, seconds, cores)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import oracle as o
+    o.build()
+    rng = np.random.default_rng(seed)
+    cores = o.num_threads()
+    # bound the sample by columns too so that the widened weight panel stays small
+    plans = []
+    for (preset, M, N, K, dt) in stages:
+        Nc = min(N, 4096)
+        plans.append((preset, M, Nc, K, dt))
+    # calibrate on 16 rows
+    def run(rows):
+        t = 0.0
+        fl = 0.0
+        for (preset, M, Nc, K, dt) in plans:
+            r = min(rows, M)
+            if dt == "bf16":
+                A = o.f32_to_bf16(rng.standard_normal((r, K)).astype(np.float32))
+                B = o.f32_to_bf16((rng.standard_normal((K, Nc)) * K ** -0.5).astype(np.float32))
+                R = o.compute_rstd(A)
+                t0 = time.perf_counter()
+                acc = o.gemm_bf16(A, B)
+                if preset == "k1":
+                    o.epilogue(acc, row=R)
+                elif preset == "k2":
+                    o.epilogue(acc, row=R, pair="swiglu", compact=True)
+                elif preset == "k4v2":
+                    o.epilogue(acc, row=R, pair="rope", cos_sin=o.rope_table(r, 128, 500000.0), cos_sin_period=128)
+                elif preset == "k0a":
+                    o.epilogue(acc, residual=o.f32_to_bf16(acc), col=np.ones(Nc, np.float32))
+                t += time.perf_counter() - t0
+            else:
+                A = rng.integers(-127, 128, (r, K), dtype=np.int8)
+                B = rng.integers(-127, 128, (K, Nc), dtype=np.int8)
+                t0 = time.perf_counter()
+                acc = o.gemm_s8(A, B)
+                o.epilogue(acc, row=np.full(r, 0.01, np.float32), col=np.full(Nc, 0.01, np.float32),
+                           bias=np.zeros(Nc, np.float32))
+                t += time.perf_counter() - t0
+            fl += 2.0 * r * Nc * K
+        return t, fl
+    t16, f16 = run(16)
+    rows = int(max(16, min(max(p[1] for p in plans), 16 * seconds_target / max(t16, 1e-3))))
+    rows = (rows // 4) * 4
+    t, fl = run(rows)
+    return fl / t / 1e12, rows, t, cores, [p[2] for p in plans]
+
+
+def run_reference_arm(args, stages):
+    """`--impl reference`: the reference's path on the host cores.  The reference itself is SYCL
+    for Intel Xe with no host implementation, so this is the CPU oracle (a port of its formulas)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = args.steps, args.warmup
+    per_step = max(0.5, min(4.0, 120.0 / max(1, steps + warm)))
+    vals = []
+    rows = cores = None
+    cols = None
+    t_all = 0.0
+    for i in range(warm + steps):
+        v, rows, t, cores, cols = cpu_sample(stages, per_step, seed=i)
+        if i >= warm:
+            vals.append(v)
+            t_all += t
+    value = sum(vals) / len(vals)
+    sample = f"{rows} rows x {cols} columns x full K per step of: {DESCR[args.workload]}"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": 1000.0 * t_all / len(vals),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "s8" if stages[0][4] == "s8" else "bf16", "data": "synthetic",
+        "config": {"workload": DESCR[args.workload], "arm": "CPU oracle (port) on host cores, OpenMP"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="k2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-unfused", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    stages = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, stages)
+        return
+
+    import torch
+    import xefuse_loader
+    xf = xefuse_loader.load()
+    capi = xf.capi
+    if not os.path.exists(capi.LIB_PATH):
+        xf.build()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the fused path has no CPU fallback "
+                         "(use --impl reference for the CPU arm)")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py --gpus N>1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    peaks = load_peaks()
+    l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
+
+    host = [gen_stage_host(st, rank, world, seed=2024 + i) for i, st in enumerate(stages)]
+    gpu = [build_stage_gpu(capi, st, h, dev) for st, h in zip(stages, host)]
+    torch.cuda.synchronize()
+    resident = sum(s["bytes_resident"] for s in gpu)
+    flush = None
+    if resident < 2 * l2_bytes:
+        flush = torch.empty(max(2 * l2_bytes, 256 << 20), dtype=torch.uint8, device=dev)
+    flops_rank = sum(s["flops"] for s in gpu)
+    flops_total = flops_rank * world
+
+    def step():
+        for s in gpu:
+            s["plan"].run()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    uuid = str(torch.cuda.get_device_properties(dev).uuid)
+    if not uuid.startswith("GPU-"):
+        uuid = "GPU-" + uuid
+    sampler = ClockSampler(uuid)
+    sampler.start()
+    time.sleep(0.15)
+    # a long enough region for the clock sampler: repeat the timed block, keep the best-of? No:
+    # EXACTLY `steps` steps are timed; the sampler simply also sees the e2e and unfused loops.
+    t0w = time.time()
+    ms = time_loop(torch, step, args.steps, flush)
+    barrier()
+    t1w = time.time()
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    for s in gpu:
+        if s["plan"].device_status() != 0:
+            raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
+    value = flops_total * args.steps / (ms * 1e-3) / 1e12
+    ms_per_step = ms / args.steps
+
+    # ---- end to end through the C ABI with host buffers
+    outs = [torch.empty(s["D"].shape, dtype=torch.bfloat16).pin_memory() for s in gpu]
+
+    def e2e_step():
+        for s, h, o in zip(gpu, host, outs):
+            s["X"].copy_(h["X"], non_blocking=True)
+            s["R"].copy_(h["R"], non_blocking=True)
+            s["plan"].run()
+            o.copy_(s["D"], non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    ms_e2e = time_loop(torch, e2e_step, args.steps)
+    barrier()
+    if dist is not None:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    e2e = {"value": flops_total * args.steps / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": int(sum(s["h2d_bytes"] for s in gpu)),
+           "d2h_bytes_per_step": int(sum(s["d2h_bytes"] for s in gpu)),
+           "ms_per_step": ms_e2e / args.steps}
+
+    # ---- unfused baseline: bare GEMM + stand-alone kernel(s)
+    unfused = None
+    if not args.no_unfused:
+        us = [build_unfused(capi, s, dev) for s in gpu]
+
+        def unfused_step():
+            for u in us:
+                u["plan"].run()
+                u["post"]()
+
+        for _ in range(3):
+            unfused_step()
+        barrier()
+        ms_u = time_loop(torch, unfused_step, args.steps, flush)
+        barrier()
+        if dist is not None:
+            t = torch.tensor([ms_u], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_u = float(t.item())
+        v_u = flops_total * args.steps / (ms_u * 1e-3) / 1e12
+        unfused = {"value": v_u, "unit": "TFLOP/s", "ms_per_step": ms_u / args.steps,
+                   "fused_speedup": value / v_u, "launches_per_step": sum(u["launches"] for u in us)}
+        del us
+    clocks = sampler.stop(t0w, time.time())
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    is_s8 = stages[0][4] == "s8"
+    peak = peaks["bf16"] * (2.0 if is_s8 else 1.0)
+    achieved = flops_rank / (ms_per_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "peak_source": ("2 x measured bf16 burst (int8 runs at twice the bf16 rate; no int8 peak was measured)"
+                                if is_s8 else f"bf16 burst, {peaks['src']}"),
+                "frac_of_sustained": achieved / (peaks["bf16_sustained"] * (2.0 if is_s8 else 1.0))
+                if peaks.get("bf16_sustained") else None,
+                "frac_of_nominal": achieved / (4500.0 if is_s8 else 2250.0),
+                "kernel": ",".join(sorted({s["plan"].kernel_name for s in gpu}))}
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            roofline["traffic"] = json.load(open(traffic_file)).get(args.workload)
+        except Exception:
+            pass
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        v, rows, t, cores, cols = cpu_sample(stages, args.cpu_seconds, seed=0)
+        cpu_baseline = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                        "sample": f"{rows} rows x {cols} columns x full K of the workload, {t:.1f} s of CPU time"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "s8" if is_s8 else "bf16", "data": "synthetic",
+        "config": {"workload": DESCR[args.workload],
+                   "sharding": f"weight columns N split {world}-way, activations and row scales replicated, no collective inside a stage",
+                   "l2": ("L2 flushed before every timed step" if flush is not None else
+                          f"resident inputs+outputs {resident >> 20} MiB > L2 {l2_bytes >> 20} MiB, no flush"),
+                   "kernels": [s["plan"].kernel_name for s in gpu]},
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "unfused": unfused,
+        "gpu_launches": args.steps * len(gpu), "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -191,3 +191,15 @@ def rope_table(M, width, theta):
     cs = np.empty((M, width), np.float32)
     lib().xo_rope_table(_p(cs), M, width, C.c_float(theta))
     return cs
+
+
+def quantize_columns_offline(W):
+    """Offline symmetric per-column int8 quantiser, restating autotune/quantize_weights_quaRot.py:176-191:
+    scale[n] = max|W[:,n]|/127 (1e-8 where that is 0); Wq = round_half_even(clip(W/scale, -128, 127)).
+    Pinned by tests/golden/quantize_columns.npz, which the reference's own function produced."""
+    W = np.asarray(W)
+    max_abs = np.abs(W).max(axis=0, keepdims=True)
+    scale = (max_abs / 127.0).squeeze(0)
+    scale = np.where(scale == 0, 1e-8, scale)
+    Wq = np.round(np.clip(W / scale[None, :], -128.0, 127.0)).astype(np.int8)
+    return Wq, scale.astype(np.float32)

@@ -1,0 +1,216 @@
+"""GPU parity: the fused tcgen05 GEMM, called through the C ABI, against the CPU oracle on the same
+seeded inputs.  int32 accumulators must be bit-exact; bf16 outputs within abs 2e-2 or rel 1e-2."""
+import numpy as np
+import pytest
+
+import parity_cases as pc
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(torch, a, dev, bf16=False):
+    if a is None:
+        return None
+    if bf16:
+        return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(dev)
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def run_gpu(capi, o, preset, d, dev, flags=0, out_dtype=None):
+    import torch
+    int8 = pc.is_int8(preset)
+    A = _t(torch, d["A"], dev, bf16=not int8)
+    B = _t(torch, d["B"], dev, bf16=not int8)
+    k = pc.epilogue_kwargs(o, preset, d)
+    M, N = A.shape[0], B.shape[1]
+    compact = bool(k.get("compact"))
+    n_out = N // 2 if compact else N
+    D = torch.full((M, n_out), float("nan"), dtype=out_dtype or torch.bfloat16, device=dev)
+    aux = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev) if k.get("want_aux") else None
+    bias = None
+    if "bias" in k:
+        bias = _t(torch, d["bias_bf16"], dev, bf16=True) if preset == "w8a8_biased_bf16bias" else _t(torch, k["bias"], dev)
+    plan = capi.GemmPlan(
+        A, B, D,
+        residual=_t(torch, k.get("residual"), dev, bf16=True), aux_store=aux,
+        row_scale=_t(torch, k.get("row"), dev), col_scale=_t(torch, k.get("col"), dev), bias=bias,
+        unary=k.get("unary", "none"), pair=k.get("pair", "none"),
+        cos_sin=_t(torch, k.get("cos_sin"), dev), cos_sin_period=k.get("cos_sin_period", 0),
+        compact=compact, flags=flags)
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    from conftest import bf16_bits
+    res = bf16_bits(D) if D.dtype == torch.bfloat16 else D.cpu().numpy()
+    return plan, res, (bf16_bits(aux) if aux is not None else None)
+
+
+def check(capi, o, preset, M, N, K, dev, flags=0, seed=0):
+    d = pc.make_inputs(o, preset, M, N, K, seed)
+    _, want = pc.expected(o, preset, d)
+    plan, got, aux = run_gpu(capi, o, preset, d, dev, flags)
+    want_aux = None
+    if isinstance(want, tuple):
+        want, want_aux = want
+    nbad, mabs, mrel = pc.compare_bf16(o, got, want)
+    assert nbad == 0, f"{preset} {M}x{N}x{K} {plan.kernel_name}: {nbad} bad, max abs {mabs}, max rel {mrel}"
+    if want_aux is not None:
+        nb2, ma2, _ = pc.compare_bf16(o, aux, want_aux)
+        assert nb2 == 0, f"{preset} aux store: {nb2} bad, max abs {ma2}"
+    return plan
+
+
+@pytest.mark.parametrize("preset", pc.PRESETS)
+def test_presets_aligned(preset, capi, oracle, cuda):
+    """Every preset at a tile-aligned shape spanning several CTA tiles and k-blocks."""
+    check(capi, oracle, preset, 384, 768, 512, cuda)
+
+
+@pytest.mark.parametrize("preset", ["k1", "k2", "k2_compact", "k4v2", "k0a", "k0_dual",
+                                    "w8a8_dequant_biased", "bias_gelu"])
+def test_presets_ragged(preset, capi, oracle, cuda):
+    """M, N, K not multiples of any tile: tails are zero-filled on load and clipped on store."""
+    check(capi, oracle, preset, 200, 336, 208, cuda)
+
+
+@pytest.mark.parametrize("flags_name", ["1cta_bn256", "2cta_bn256", "1cta_bn128", "2cta_bn128", "direct"])
+@pytest.mark.parametrize("preset", ["k2_compact", "k4v2_table", "k0a"])
+def test_every_kernel_variant(preset, flags_name, capi, oracle, cuda):
+    f = {"1cta_bn256": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN256,
+         "2cta_bn256": capi.FLAG_FORCE_2CTA | capi.FLAG_FORCE_BN256,
+         "1cta_bn128": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN128,
+         "2cta_bn128": capi.FLAG_FORCE_2CTA | capi.FLAG_FORCE_BN128,
+         "direct": capi.FLAG_DIRECT_STORE}[flags_name]
+    check(capi, oracle, preset, 512, 1024, 320, cuda, flags=f)
+
+
+@pytest.mark.parametrize("flags_name", ["1cta_bn256", "2cta_bn256", "1cta_bn128"])
+def test_int8_variants(flags_name, capi, oracle, cuda):
+    f = {"1cta_bn256": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN256,
+         "2cta_bn256": capi.FLAG_FORCE_2CTA | capi.FLAG_FORCE_BN256,
+         "1cta_bn128": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN128}[flags_name]
+    check(capi, oracle, "w8a8_dequant_biased", 512, 1024, 640, cuda, flags=f)
+
+
+@pytest.mark.parametrize("shape", [(384, 768, 1024), (200, 336, 208), (128, 256, 128), (1, 16, 16)])
+@pytest.mark.parametrize("flags", [0, 2, 4])
+def test_int32_accumulator_bit_exact(shape, flags, capi, oracle, cuda):
+    """Raw int32 accumulators (empty epilogue, int32 D) equal the exact integer GEMM."""
+    import torch
+    M, N, K = shape
+    rng = np.random.default_rng(11)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    want = oracle.gemm_s8(A, B)
+    D = torch.full((M, N), -7, dtype=torch.int32, device=cuda)
+    plan = capi.GemmPlan(torch.from_numpy(A).to(cuda), torch.from_numpy(B).to(cuda), D, flags=flags)
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    assert np.array_equal(D.cpu().numpy(), want), plan.kernel_name
+
+
+def test_int32_extremes(capi, oracle, cuda):
+    """All -128 inputs: the largest magnitude products, K up to the Llama-70B FFN depth."""
+    import torch
+    M, N, K = 128, 256, 28672
+    A = torch.full((M, K), -128, dtype=torch.int8, device=cuda)
+    B = torch.full((K, N), -128, dtype=torch.int8, device=cuda)
+    D = torch.zeros((M, N), dtype=torch.int32, device=cuda)
+    plan = capi.GemmPlan(A, B, D)
+    plan.run()
+    torch.cuda.synchronize()
+    assert int(D.min()) == int(D.max()) == K * 16384
+
+
+def test_fp32_accumulator_output(capi, oracle, cuda):
+    """fp32 D with an empty epilogue returns the accumulator itself."""
+    import torch
+    d = pc.make_inputs(oracle, "identity", 256, 512, 384, 3)
+    acc = oracle.gemm_bf16(d["A"], d["B"])
+    _, got, _ = run_gpu(capi, oracle, "identity", d, cuda, out_dtype=torch.float32)
+    assert np.abs(got - acc).max() < 1e-4 * np.abs(acc).max()
+
+
+def test_batched_L(capi, oracle, cuda):
+    """L > 1 with per-batch A, B, D and vectors; and a shared weight (batch stride 0)."""
+    import torch
+    from conftest import bf16_bits
+    L, M, N, K = 3, 160, 256, 192
+    rng = np.random.default_rng(5)
+    A = oracle.f32_to_bf16(rng.standard_normal((L, M, K)).astype(np.float32))
+    B = oracle.f32_to_bf16((rng.standard_normal((L, K, N)) * K ** -0.5).astype(np.float32))
+    R = rng.uniform(0.5, 1.5, (L, M)).astype(np.float32)
+    tA, tB = _t(torch, A, cuda, True), _t(torch, B, cuda, True)
+    D = torch.zeros((L, M, N), dtype=torch.bfloat16, device=cuda)
+    plan = capi.GemmPlan(tA, tB, D, row_scale=_t(torch, R.reshape(-1), cuda), pair="swiglu")
+    plan.run()
+    torch.cuda.synchronize()
+    got = bf16_bits(D)
+    for l in range(L):
+        want = oracle.epilogue(oracle.gemm_bf16(A[l], B[l]), row=R[l], pair="swiglu")
+        assert pc.compare_bf16(oracle, got[l], want)[0] == 0
+    # shared B: 2-D weight tensor => batch stride 0
+    D2 = torch.zeros((L, M, N), dtype=torch.bfloat16, device=cuda)
+    plan2 = capi.GemmPlan(tA, tB[1].contiguous(), D2, row_scale=_t(torch, R.reshape(-1), cuda))
+    plan2.run()
+    torch.cuda.synchronize()
+    got2 = bf16_bits(D2)
+    for l in range(L):
+        want = oracle.epilogue(oracle.gemm_bf16(A[l], B[1]), row=R[l])
+        assert pc.compare_bf16(oracle, got2[l], want)[0] == 0
+
+
+def test_null_vector_uses_null_default(capi, oracle, cuda):
+    """A broadcast node with a null pointer contributes its null_default (ColBroadcast semantics)."""
+    import torch
+    import ctypes as C
+    from conftest import bf16_bits
+    d = pc.make_inputs(oracle, "k1", 128, 256, 128, 9)
+    A, B = _t(torch, d["A"], cuda, True), _t(torch, d["B"], cuda, True)
+    D = torch.zeros((128, 256), dtype=torch.bfloat16, device=cuda)
+    plan = capi.GemmPlan(A, B, D)
+    plan.close()
+    desc = plan.desc
+    desc.epi.row_scale.enabled = 1
+    desc.epi.row_scale.ptr = None
+    desc.epi.row_scale.dtype = capi.DT_F32
+    desc.epi.row_scale.null_default = 0.5
+    h = C.c_void_p()
+    capi.check(capi.lib().xf_gemm_plan_create(C.byref(desc), plan.workspace.data_ptr(), C.byref(h)))
+    capi.check(capi.lib().xf_gemm_run(h, None))
+    torch.cuda.synchronize()
+    capi.lib().xf_plan_destroy(h)
+    want = oracle.epilogue(oracle.gemm_bf16(d["A"], d["B"]), row=np.full(128, 0.5, np.float32))
+    assert pc.compare_bf16(oracle, bf16_bits(D), want)[0] == 0
+
+
+def test_rerun_is_idempotent(capi, oracle, cuda):
+    """run() is re-entrant with the same plan: 20 back-to-back launches leave the same bits."""
+    import torch
+    from conftest import bf16_bits
+    d = pc.make_inputs(oracle, "k0a", 512, 512, 256, 4)
+    plan, first, _ = run_gpu(capi, oracle, "k0a", d, cuda)
+    for _ in range(20):
+        plan.run()
+    torch.cuda.synchronize()
+    D = plan._keep[2]
+    assert np.array_equal(bf16_bits(D), first)
+
+
+def test_canary_rows_and_columns_untouched(capi, oracle, cuda):
+    """D embedded in a larger buffer (ldd > N, rows after M): nothing outside [M,N] is written."""
+    import torch
+    from conftest import bf16_bits
+    M, N, K, LDD = 200, 328, 136, 344
+    d = pc.make_inputs(oracle, "k1", M, N, K, 6)
+    A, B = _t(torch, d["A"], cuda, True), _t(torch, d["B"], cuda, True)
+    for flags in (0, capi.FLAG_DIRECT_STORE):
+        buf = torch.full((M + 8, LDD), 777.0, dtype=torch.bfloat16, device=cuda)
+        D = buf[:M, :N]
+        plan = capi.GemmPlan(A, B, D, row_scale=_t(torch, d["scale"], cuda), flags=flags)
+        plan.run()
+        torch.cuda.synchronize()
+        want = oracle.epilogue(oracle.gemm_bf16(d["A"], d["B"]), row=d["scale"])
+        assert pc.compare_bf16(oracle, bf16_bits(buf[:M, :N].contiguous()), want)[0] == 0
+        assert bool((buf[M:, :] == 777.0).all()) and bool((buf[:, N:] == 777.0).all())

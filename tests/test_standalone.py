@@ -1,0 +1,111 @@
+"""GPU parity of the stand-alone (unfused) elementwise kernels and the row-reduction producers
+against the oracle.  bf16 in, fp32 math, one rounding: results should match to 1 bf16 ulp."""
+import numpy as np
+import pytest
+
+import parity_cases as pc
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(torch, bits, dev):
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).to(dev)
+
+
+def _f(torch, a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+@pytest.fixture(scope="module", params=[(96, 256), (50, 136), (33, 70)], ids=["vec8", "vec8_ragged_rows", "pairs"])
+def data(request, oracle):
+    M, N = request.param
+    rng = np.random.default_rng(M * 1000 + N)
+    d = dict(M=M, N=N)
+    d["x"] = oracle.f32_to_bf16(rng.standard_normal((M, N)).astype(np.float32) * 2.0)
+    d["res"] = oracle.f32_to_bf16(rng.standard_normal((M, N)).astype(np.float32))
+    d["row"] = rng.uniform(0.5, 1.5, M).astype(np.float32)
+    d["col"] = rng.uniform(0.8, 1.2, N).astype(np.float32)
+    d["cs"] = oracle.rope_table(M, N, 10000.0)
+    d["xf"] = oracle.bf16_to_f32(d["x"])
+    return d
+
+
+def _check(oracle, got_t, want_bits):
+    from conftest import bf16_bits
+    nbad, mabs, mrel = pc.compare_bf16(oracle, bf16_bits(got_t), want_bits)
+    assert nbad == 0, (mabs, mrel)
+    # tighter: at most one bf16 ulp apart
+    g = oracle.bf16_to_f32(bf16_bits(got_t)).astype(np.float64)
+    w = oracle.bf16_to_f32(want_bits).astype(np.float64)
+    assert np.all(np.abs(g - w) <= np.maximum(np.abs(w), 1e-30) * 2 ** -7 + 1e-30)
+
+
+def test_elementwise_ops(data, capi, oracle, cuda):
+    import torch
+    d, o = data, oracle
+    x = lambda: _bf(torch, d["x"], cuda)
+    row, col, res, cs = _f(torch, d["row"], cuda), _f(torch, d["col"], cuda), _bf(torch, d["res"], cuda), _f(torch, d["cs"], cuda)
+
+    t = x(); capi.sa_scale_rows(t, row); _check(o, t, o.epilogue(d["xf"], row=d["row"]))
+    t = x(); capi.sa_scale_cols(t, col); _check(o, t, o.epilogue(d["xf"], col=d["col"]))
+    t = x(); capi.sa_add_residual(t, res); _check(o, t, o.epilogue(d["xf"], residual=d["res"]))
+    t = x(); capi.sa_residual_gamma(t, res, col); _check(o, t, o.epilogue(d["xf"], residual=d["res"], col=d["col"]))
+    t = x(); capi.sa_swiglu(t); _check(o, t, o.epilogue(d["xf"], pair="swiglu"))
+    t = x(); capi.sa_geglu(t); _check(o, t, o.epilogue(d["xf"], pair="geglu"))
+    t = x(); capi.sa_bias_add(t, col); _check(o, t, o.epilogue(d["xf"], bias=d["col"]))
+    for name in ["gelu", "gelu_tanh", "silu", "relu", "sigmoid"]:
+        t = x(); capi.sa_unary(t, name); _check(o, t, o.epilogue(d["xf"], unary=name))
+    src = x(); out = torch.zeros_like(src)
+    capi.sa_rope(out, src, cs); _check(o, out, o.epilogue(d["xf"], pair="rope", cos_sin=d["cs"]))
+    out = torch.zeros_like(src)
+    capi.sa_rope_scaled(out, src, row, cs)
+    _check(o, out, o.epilogue(d["xf"], row=d["row"], pair="rope", cos_sin=d["cs"]))
+
+
+def test_dequant_w8a8(data, capi, oracle, cuda):
+    import torch
+    d = data
+    rng = np.random.default_rng(7)
+    acc = rng.integers(-2 ** 24, 2 ** 24, (d["M"], d["N"]), dtype=np.int32)
+    st = (d["row"] * 1e-3).astype(np.float32)
+    sc = (d["col"] * 1e-3).astype(np.float32)
+    out = torch.zeros((d["M"], d["N"]), dtype=torch.bfloat16, device=cuda)
+    capi.sa_dequant_w8a8(out, _f(torch, acc, cuda), _f(torch, st, cuda), _f(torch, sc, cuda))
+    _check(oracle, out, oracle.preset_w8a8(acc, st, sc))
+
+
+def test_batched_standalone(capi, oracle, cuda):
+    import torch
+    from conftest import bf16_bits
+    L, M, N = 3, 20, 64
+    rng = np.random.default_rng(8)
+    x = oracle.f32_to_bf16(rng.standard_normal((L, M, N)).astype(np.float32))
+    row = rng.uniform(0.5, 1.5, (L, M)).astype(np.float32)
+    t = _bf(torch, x, cuda)
+    capi.sa_scale_rows(t, _f(torch, row.reshape(-1), cuda))
+    got = bf16_bits(t)
+    for l in range(L):
+        want = oracle.epilogue(oracle.bf16_to_f32(x[l]), row=row[l])
+        assert np.array_equal(got[l], want)
+
+
+@pytest.mark.parametrize("shape", [(64, 4096), (7, 200), (3, 33)])
+def test_rstd_and_quantize(shape, capi, oracle, cuda):
+    import torch
+    M, N = shape
+    rng = np.random.default_rng(M + N)
+    x = oracle.f32_to_bf16(rng.standard_normal((M, N)).astype(np.float32) * 3.0)
+    tx = _bf(torch, x, cuda)
+    r = torch.zeros(M, dtype=torch.float32, device=cuda)
+    capi.compute_rstd(tx, r)
+    want_r = oracle.compute_rstd(x)
+    assert np.allclose(r.cpu().numpy(), want_r, rtol=2e-6)
+    xq = torch.zeros((M, N), dtype=torch.int8, device=cuda)
+    st = torch.zeros(M, dtype=torch.float32, device=cuda)
+    capi.compute_rstd_and_quantize(tx, xq, st)
+    want_q, want_st = oracle.rstd_and_quantize(x, want_r)
+    assert np.allclose(st.cpu().numpy(), want_st, rtol=1e-5)
+    # the rstd of the two paths may differ in the last bit, which can move a value that sits on a
+    # rounding boundary by one step
+    diff = np.abs(xq.cpu().numpy().astype(np.int32) - want_q.astype(np.int32))
+    assert diff.max() <= 1 and (diff > 0).mean() < 1e-3
