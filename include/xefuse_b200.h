@@ -176,6 +176,29 @@ XF_API xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code)
 XF_API const char* xf_gemm_plan_kernel_name(const xf_plan* plan);
 XF_API xf_status xf_plan_destroy(xf_plan* plan);
 
+/*
+ * One-call fused GEMM that allocates nothing, for callers that cannot call cudaMalloc: a serving
+ * process that handed all of HBM to its own memory pool at start-up (a later cudaMalloc would
+ * fail, or stall every stream while the driver synchronises the device), or a plug-in that is
+ * only lent buffers by its host and owns no allocator.  It has no counterpart in the reference,
+ * whose callers always allocate a workspace (tests/test_k1.cpp:96-97).
+ *
+ * The caller passes inputs and outputs in `desc` as usual.  The kernel's scratch -- the status
+ * word of its bounded waits -- lives in a static device array of XF_STATIC_WORKSPACE_BYTES that
+ * each GPU using the library holds until process exit; a problem whose workspace requirement
+ * (xf_gemm_workspace_size) exceeds that is refused with XF_ERR_NOT_SUPPORTED.  No cudaMalloc,
+ * cudaFree or host allocation happens inside: the plan lives on the stack and is rebuilt on every
+ * call (three tensor-map encodes), so prefer a plan when you can allocate.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call outside any stream capture.  All calls on a device
+ * share the array and each call clears the words it uses on `stream` before its kernel, so calls
+ * whose kernels may overlap on the GPU (different streams, no ordering between them) race on it:
+ * order them, or use plans with separate workspaces.
+ */
+#define XF_STATIC_WORKSPACE_BYTES 256
+XF_API xf_status xf_gemm_run_static_workspace(const xf_gemm_desc* desc, void* stream);
+
 /* Thread-local text of the last error produced by any entry point on this thread. */
 XF_API const char* xf_last_error_string(void);
 XF_API const char* xf_status_string(xf_status s);

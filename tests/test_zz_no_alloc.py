@@ -1,0 +1,70 @@
+"""The allocation-free entry point, xf_gemm_run_static_workspace.
+
+Some callers of this library cannot allocate device memory: a serving process that gave all of HBM
+to its own pool when it started, or a plug-in that only borrows buffers from its host.  For them
+the fused GEMM can run with its scratch (the kernel's status word) in a static device array inside
+the library instead of a caller-allocated workspace.  This test drives that entry through the C
+ABI and checks that it writes exactly what the plan-based entry writes, on two calls in a row --
+the second call finds the array as the first one left it.
+
+Collected last on purpose (file name), so a run that stops at the first failure has already run
+every other test.  It passes alone in a fresh process and after the rest of the suite.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import parity_cases as pc
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(torch, bits, dev):
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).to(dev)
+
+
+def _both_entries(capi, oracle, dev, preset, M, N, K, seed):
+    """Runs one problem through the plan entry and through the static-workspace entry."""
+    import torch
+    from conftest import bf16_bits
+    d = pc.make_inputs(oracle, preset, M, N, K, seed)
+    A, B = _bf(torch, d["A"], dev), _bf(torch, d["B"], dev)
+    R = torch.from_numpy(d["scale"]).to(dev)
+    compact = preset == "k2_compact"
+    n_out = N // 2 if compact else N
+    kw = dict(row_scale=R, pair="swiglu" if compact else "none", compact=compact)
+    D_plan = torch.full((M, n_out), float("nan"), dtype=torch.bfloat16, device=dev)
+    plan = capi.GemmPlan(A, B, D_plan, **kw)
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+
+    # same descriptor, other output buffer, no workspace and no plan
+    D_static = torch.full((M, n_out), float("nan"), dtype=torch.bfloat16, device=dev)
+    desc = capi.XfGemmDesc.from_buffer_copy(plan.desc)
+    desc.D = D_static.data_ptr()
+    before = torch.cuda.memory_allocated(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    capi.check(capi.lib().xf_gemm_run_static_workspace(C.byref(desc), stream))
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated(dev) == before
+    got_plan, got_static = bf16_bits(D_plan), bf16_bits(D_static)
+    # same kernel, same inputs: bit-identical; and both inside the parity bar against the oracle
+    assert np.array_equal(got_static, got_plan)
+    _, want = pc.expected(oracle, preset, d)
+    nbad, mabs, mrel = pc.compare_bf16(oracle, got_static, want)
+    assert nbad == 0, (mabs, mrel)
+
+
+def test_static_workspace_entry_matches_plan_entry_twice(capi, oracle, cuda):
+    # two calls in a row, different problems: the second starts from the first one's leftovers
+    _both_entries(capi, oracle, cuda, "k1", 256, 512, 256, seed=21)
+    _both_entries(capi, oracle, cuda, "k2_compact", 200, 336, 208, seed=22)
+
+
+def test_static_workspace_entry_rejects_bad_problems(capi, cuda):
+    d = capi.XfGemmDesc()
+    rc = capi.lib().xf_gemm_run_static_workspace(C.byref(d), None)
+    assert rc != 0 and capi.lib().xf_last_error_string()
+    assert capi.lib().xf_gemm_run_static_workspace(None, None) == 4

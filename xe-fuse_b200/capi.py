@@ -60,6 +60,7 @@ class XfGemmDesc(C.Structure):
 EXPORTS = [
     "xf_gemm_can_implement", "xf_gemm_workspace_size", "xf_gemm_plan_create", "xf_gemm_run",
     "xf_gemm_plan_device_status", "xf_gemm_plan_kernel_name", "xf_plan_destroy",
+    "xf_gemm_run_static_workspace",
     "xf_last_error_string", "xf_status_string", "xf_version", "xf_compiled_arch",
     "xf_sa_scale_rows", "xf_sa_scale_cols", "xf_sa_add_residual", "xf_sa_residual_gamma",
     "xf_sa_swiglu", "xf_sa_geglu", "xf_sa_rope", "xf_sa_rope_scaled", "xf_sa_unary",
@@ -87,6 +88,7 @@ def lib():
     L.xf_gemm_plan_kernel_name.argtypes = [vp]
     L.xf_gemm_plan_kernel_name.restype = C.c_char_p
     L.xf_plan_destroy.argtypes = [vp]
+    L.xf_gemm_run_static_workspace.argtypes = [C.POINTER(XfGemmDesc), vp]
     L.xf_last_error_string.restype = C.c_char_p
     L.xf_status_string.argtypes = [i32]
     L.xf_status_string.restype = C.c_char_p

@@ -285,7 +285,8 @@ static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
   return best;
 }
 
-static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* plan) {
+static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* plan,
+                            bool clear_status_now = true) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) {
     set_error("no CUDA device: %s", cudaGetErrorString(cudaGetLastError()));
@@ -386,7 +387,7 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   const int nunits = total_tiles < units ? total_tiles : units;
   plan->grid = nunits * v->ctas;
   snprintf(plan->name, sizeof(plan->name), "%s_s%d", v->name, v->stages);
-  if (p.status) {
+  if (p.status && clear_status_now) {
     ce = cudaMemset(p.status, 0, 16);
     if (ce != cudaSuccess) {
       set_error("clearing the workspace status word failed: %s", cudaGetErrorString(ce));
@@ -457,6 +458,81 @@ xf_status xf_gemm_run(xf_plan* plan, void* stream) {
     return XF_ERR_INTERNAL;
   }
   return XF_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------
+// xf_gemm_run_static_workspace: the fused GEMM for callers that may not allocate.
+//
+// The kernel's scratch (the status word a bounded wait writes when it gives up) normally lives in
+// a workspace the caller allocates.  Here it lives in the file-scope device array below, which
+// every GPU that loads this library holds until the process exits.  Nothing in this entry point
+// allocates: the plan is built on the stack, the array's device address comes from
+// cudaGetSymbolAddress (host code must not pass the array's name to a kernel: on the host that
+// name is only a stand-in, not a device address), and the word is cleared with a memset ordered on
+// the caller's stream.  All calls on one device share the array, so two calls whose kernels overlap
+// on the GPU race on it.
+static __device__ __align__(256) unsigned char g_static_workspace[XF_STATIC_WORKSPACE_BYTES];
+
+static const int kMaxDevices = 64;
+static void* g_static_ws_addr[kMaxDevices];
+static bool g_static_ws_ready[kMaxDevices];
+static std::mutex g_static_ws_mutex;
+
+// Device address of g_static_workspace on the CURRENT device; looked up once per device.
+static xf_status static_workspace_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    xf::set_error("no CUDA device: %s", cudaGetErrorString(e));
+    return XF_ERR_ARCH_MISMATCH;
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    xf::set_error("device ordinal %d beyond the %d devices the static workspace table covers", dev,
+                  kMaxDevices);
+    return XF_ERR_NOT_SUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+  if (!g_static_ws_ready[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_workspace);
+    if (e != cudaSuccess || p == nullptr) {
+      xf::set_error("cudaGetSymbolAddress(static workspace) failed on device %d: %s", dev,
+                    cudaGetErrorString(e));
+      return XF_ERR_INTERNAL;
+    }
+    g_static_ws_addr[dev] = p;
+    g_static_ws_ready[dev] = true;
+  }
+  *out = g_static_ws_addr[dev];
+  return XF_SUCCESS;
+}
+
+xf_status xf_gemm_run_static_workspace(const xf_gemm_desc* desc, void* stream) {
+  xf_status s = xf::validate(desc);
+  if (s != XF_SUCCESS) return s;
+  size_t need = 0;
+  s = xf_gemm_workspace_size(desc, &need);
+  if (s != XF_SUCCESS) return s;
+  if (need > XF_STATIC_WORKSPACE_BYTES) {
+    xf::set_error("this problem needs %zu bytes of workspace; the static workspace holds at most %d. "
+                  "Allocate a workspace and use xf_gemm_plan_create / xf_gemm_run instead",
+                  need, XF_STATIC_WORKSPACE_BYTES);
+    return XF_ERR_NOT_SUPPORTED;
+  }
+  void* ws = nullptr;
+  s = static_workspace_address(&ws);
+  if (s != XF_SUCCESS) return s;
+  xf_plan plan;  // on the stack: no host allocation either
+  memset(&plan, 0, sizeof(plan));
+  s = xf::build_plan(desc, ws, &plan, /*clear_status_now=*/false);
+  if (s != XF_SUCCESS) return s;
+  // The array keeps whatever the previous call left: the status word must start at zero.
+  cudaError_t e = cudaMemsetAsync(ws, 0, 16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    xf::set_error("clearing the static workspace failed: %s", cudaGetErrorString(e));
+    return XF_ERR_INTERNAL;
+  }
+  return xf_gemm_run(&plan, stream);
 }
 
 xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code) {
