@@ -236,6 +236,23 @@ XF_API xf_status xf_compute_rstd(const void* x, float* rstd, int M, int N, int L
 XF_API xf_status xf_compute_rstd_and_quantize(const void* x, int8_t* xq, float* scale_token,
                                               int M, int N, int L, float eps, void* stream);
 
+/*
+ * Harness utilities behind the front end's cutlass/util shims (not on the fused path): the
+ * seeded fill the harness mains call initialize_block, the naive device GEMM they use to rebuild
+ * the expected accumulator (cutlass::reference::device::GemmComplex in tests/test_k1.cpp:113-117)
+ * and the relative comparison (BlockCompareRelativelyEqual, tests/test_k1.cpp:138-140).
+ */
+XF_API xf_status xf_harness_fill_uniform(int dtype, void* ptr, long long n, uint64_t seed, int lo,
+                                         int hi, void* stream);
+XF_API xf_status xf_harness_ref_gemm(int dtype_a, const void* A, int64_t lda, int64_t batch_a,
+                                     int dtype_b, const void* B, int64_t ldb, int64_t batch_b,
+                                     int dtype_c, const void* C, int64_t ldc, int64_t batch_c,
+                                     int dtype_d, void* D, int64_t ldd, int64_t batch_d, int M, int N,
+                                     int K, int L, float alpha, float beta, void* stream);
+XF_API xf_status xf_harness_compare(int dtype, const void* a, const void* b, long long n,
+                                    float epsilon, float nonzero_floor, long long* mismatches,
+                                    void* stream);
+
 #ifdef __cplusplus
 }
 #endif

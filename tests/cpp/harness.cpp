@@ -1,0 +1,373 @@
+// Harness main in the style of the reference's tests/test_k*.cpp, written against the front end
+// (xe_fuse::builder, xe_fuse::Gemm* named kernels, cutlass/util shims):
+//
+//   harness --preset=<name> [--m=..] [--n=..] [--k=..] [--l=..] [--iterations=..]
+//
+// For one preset it fills seeded inputs, runs the fused kernel through the builder API, rebuilds
+// the expected result (device reference GEMM in fp32 + the preset's formula on the host) and prints
+// "Disposition: Passed|Failed" -- the line the reference's harnesses print -- plus a TFlop/s line.
+// Parity bar: |got - want| <= 2e-2 or <= 1e-2 * |want| per element.
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <iostream>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "xe-fuse/builder/epilogue_builder.hpp"
+#include "xe-fuse/kernels/compute_rstd.hpp"
+#include "xe-fuse/kernels/gemm_dequant_rope.hpp"
+#include "xe-fuse/kernels/gemm_dequant_swiglu.hpp"
+#include "xe-fuse/kernels/gemm_dequant_w8a8.hpp"
+#include "xe-fuse/kernels/gemm_dual_output.hpp"
+#include "xe-fuse/kernels/gemm_moe_expert.hpp"
+#include "xe-fuse/kernels/gemm_residual_gamma.hpp"
+#include "xe-fuse/kernels/gemm_rmsnorm.hpp"
+#include "xe-fuse/kernels/gemm_rmsnorm_rope.hpp"
+#include "xe-fuse/kernels/gemm_rmsnorm_swiglu.hpp"
+#include "xe-fuse/kernels/gemm_rope.hpp"
+#include "xe-fuse/kernels/gemm_swiglu.hpp"
+
+#include "cutlass/util/GPU_Clock.hpp"
+#include "cutlass/util/command_line.h"
+#include "cutlass/util/device_memory.h"
+#include "cutlass/util/packed_stride.hpp"
+#include "cutlass/util/reference/device/gemm_complex.h"
+#include "cutlass/util/reference/device/tensor_compare.h"
+#include "helper.h"
+#include "sycl_common.hpp"
+
+using namespace cute;
+namespace b = xe_fuse::builder;
+using bf16 = cutlass::bfloat16_t;
+using TileShape = Shape<_256, _256, _32>;
+using PackedMN = b::PackedMN;
+
+struct Problem {
+  int M = 384, N = 512, K = 256, L = 1, iterations = 0;
+  std::string preset = "k1";
+};
+
+// Everything a preset may need, allocated once per run.
+struct Buffers {
+  cutlass::DeviceAllocation<bf16> A, B, D, aux, residual;
+  cutlass::DeviceAllocation<int8_t> Ai, Bi;
+  cutlass::DeviceAllocation<float> acc, row, col, bias, cos_sin;
+};
+
+template <class T>
+static void fill_gauss(T* p, size_t n, unsigned seed, float sigma, float mean = 0.f) {
+  std::mt19937 rng(seed);
+  std::normal_distribution<float> d(mean, sigma);
+  for (size_t i = 0; i < n; ++i) p[i] = T(d(rng));
+}
+
+static void fill_int8(int8_t* p, size_t n, unsigned seed) {
+  std::mt19937 rng(seed);
+  std::uniform_int_distribution<int> d(-64, 63);   // range of the reference's W8A8 tests
+  for (size_t i = 0; i < n; ++i) p[i] = static_cast<int8_t>(d(rng));
+}
+
+// Runs one Gemm type; `expect(m, n, acc_row) -> value` gives the fp32 expected output element.
+template <class GemmOp, class EvtArgs>
+static bool run_case(Problem const& P, Buffers& buf, EvtArgs const& evt_args, bool int8,
+                     std::function<float(int, int, int, const float*)> expect, bool compact = false,
+                     xefuse::Extensions ext = {}, bool check_aux = false) {
+  const int M = P.M, N = P.N, K = P.K, L = P.L;
+  using Kernel = typename GemmOp::GemmKernel;
+  auto sA = cutlass::make_cute_packed_stride(typename Kernel::StrideA{}, make_shape(M, K, L));
+  auto sB = cutlass::make_cute_packed_stride(typename Kernel::StrideB{}, make_shape(N, K, L));
+  const int n_out = compact ? N / 2 : N;
+  auto sD = cutlass::make_cute_packed_stride(PackedMN{}, make_shape(M, n_out, L));
+
+  typename Kernel::EpilogueArguments epi{evt_args, nullptr, sD, buf.D.get(), sD};
+  typename Kernel::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, L}, {}, epi, {}};
+  if constexpr (std::is_same<typename Kernel::ElementA, int8_t>::value)
+    args.mainloop = {buf.Ai.get(), sA, buf.Bi.get(), sB};
+  else
+    args.mainloop = {buf.A.get(), sA, buf.B.get(), sB};
+
+  GemmOp op;
+  ext.compact_pair_output = compact;
+  op.set_extensions(ext);
+  cutlass::device_memory::allocation<uint8_t> workspace(GemmOp::get_workspace_size(args));
+  CUTLASS_CHECK(GemmOp::can_implement(args, ext));
+  CUTLASS_CHECK(op.initialize(args, workspace.get()));
+  CUTLASS_CHECK(op.run());
+  compat::wait();
+  if (op.device_status() != 0) {
+    std::cout << "device status " << op.device_status() << "\nDisposition: Failed" << std::endl;
+    return false;
+  }
+
+  // expected accumulator on the device, fp32
+  if (int8) {
+    cutlass::TensorRef rA(buf.Ai.get(), cutlass::layout::RowMajor::packed({M, K}));
+    cutlass::TensorRef rB(buf.Bi.get(), cutlass::layout::RowMajor::packed({K, N}));
+    cutlass::TensorRef rC(buf.acc.get(), cutlass::layout::RowMajor::packed({M, N}));
+    cutlass::reference::device::GemmComplex({M, N, K}, 1.0f, rA, cutlass::ComplexTransform::kNone, rB,
+                                            cutlass::ComplexTransform::kNone, 0.0f, rC, rC, 0.0f, L,
+                                            int64_t(M) * K, int64_t(K) * N, int64_t(M) * N, int64_t(M) * N);
+  } else {
+    cutlass::TensorRef rA(buf.A.get(), cutlass::layout::RowMajor::packed({M, K}));
+    cutlass::TensorRef rB(buf.B.get(), cutlass::layout::RowMajor::packed({K, N}));
+    cutlass::TensorRef rC(buf.acc.get(), cutlass::layout::RowMajor::packed({M, N}));
+    cutlass::reference::device::GemmComplex({M, N, K}, 1.0f, rA, cutlass::ComplexTransform::kNone, rB,
+                                            cutlass::ComplexTransform::kNone, 0.0f, rC, rC, 0.0f, L,
+                                            int64_t(M) * K, int64_t(K) * N, int64_t(M) * N, int64_t(M) * N);
+  }
+  compat::wait();
+
+  long long bad = 0;
+  double max_abs = 0;
+  const float* acc = buf.acc.get();
+  const bf16* got = buf.D.get();
+  for (int l = 0; l < L; ++l)
+    for (int m = 0; m < M; ++m) {
+      const float* arow = acc + (size_t(l) * M + m) * N;
+      for (int j = 0; j < n_out; ++j) {
+        const float want = expect(l, m, compact ? 2 * j : j, arow);
+        const float g = float(got[(size_t(l) * M + m) * n_out + j]);
+        const double err = std::fabs(double(g) - double(want));
+        if (err > max_abs) max_abs = err;
+        if (!(err <= 2e-2 || err <= 1e-2 * std::fabs(want))) {
+          if (bad < 5) std::printf("  mismatch l=%d m=%d n=%d got=%g want=%g\n", l, m, j, g, want);
+          ++bad;
+        }
+      }
+    }
+  if (check_aux) {  // aux = bf16(acc + residual)
+    const bf16* aux = buf.aux.get();
+    const bf16* res = buf.residual.get();
+    for (size_t i = 0; i < size_t(L) * M * N; ++i) {
+      const float want = acc[i] + float(res[i]);
+      const double err = std::fabs(double(float(aux[i])) - double(want));
+      if (!(err <= 2e-2 || err <= 1e-2 * std::fabs(want))) ++bad;
+    }
+  }
+  std::printf("kernel: %s  max_abs_err: %.4g  mismatches: %lld\n", op.kernel_name(), max_abs, bad);
+  std::cout << "Disposition: " << (bad == 0 ? "Passed" : "Failed") << std::endl;
+
+  if (P.iterations > 0) {
+    GPU_Clock timer;
+    timer.start();
+    for (int i = 0; i < P.iterations; ++i) op.run();
+    compat::wait();
+    const float time_s = timer.seconds() / P.iterations;
+    const double tflops = 2.0 * M * N * K * L * 1e-12;
+    std::cout << "Problem Size: " << M << 'x' << N << 'x' << K << 'x' << L << std::endl;
+    std::printf("%s: [%4.3f]TFlop/s  (%6.4f)ms\n", P.preset.c_str(), tflops / time_s, time_s * 1000);
+  }
+  return bad == 0;
+}
+
+static float silu(float x) { return x / (1.0f + std::exp(-x)); }
+static float gelu(float x) { return x * 0.5f * (1.0f + std::erf(x * 0.7071067811865475f)); }
+
+int main(int argc, const char** argv) {
+  Problem P;
+  cutlass::CommandLine cmd(argc, argv);
+  cmd.get_cmd_line_argument("preset", P.preset, std::string("k1"));
+  cmd.get_cmd_line_argument("m", P.M, 384);
+  cmd.get_cmd_line_argument("n", P.N, 512);
+  cmd.get_cmd_line_argument("k", P.K, 256);
+  cmd.get_cmd_line_argument("l", P.L, 1);
+  cmd.get_cmd_line_argument("iterations", P.iterations, 0);
+  const int M = P.M, N = P.N, K = P.K, L = P.L;
+  const std::string& p = P.preset;
+  const bool int8 = p.rfind("w8a8", 0) == 0;
+
+  Buffers buf;
+  buf.D.reset(size_t(M) * N * L);
+  buf.acc.reset(size_t(M) * N * L);
+  buf.row.reset(size_t(M) * L);
+  buf.col.reset(size_t(N) * L);
+  buf.bias.reset(size_t(N) * L);
+  buf.cos_sin.reset(size_t(M) * N * L);
+  buf.residual.reset(size_t(M) * N * L);
+  buf.aux.reset(size_t(M) * N * L);
+  if (int8) {
+    buf.Ai.reset(size_t(M) * K * L);
+    buf.Bi.reset(size_t(K) * N * L);
+    fill_int8(buf.Ai.get(), buf.Ai.size(), 1001);
+    fill_int8(buf.Bi.get(), buf.Bi.size(), 1002);
+  } else {
+    buf.A.reset(size_t(M) * K * L);
+    buf.B.reset(size_t(K) * N * L);
+    fill_gauss(buf.A.get(), buf.A.size(), 2023, 1.0f);
+    fill_gauss(buf.B.get(), buf.B.size(), 2022, 1.0f / std::sqrt(float(K)));
+  }
+  {
+    std::mt19937 rng(42);
+    std::uniform_real_distribution<float> d(0.5f, 1.5f), g(0.8f, 1.2f), q(0.001f, 0.01f);
+    for (size_t i = 0; i < buf.row.size(); ++i) buf.row.get()[i] = int8 ? q(rng) : d(rng);
+    for (size_t i = 0; i < buf.col.size(); ++i) buf.col.get()[i] = int8 ? q(rng) : g(rng);
+  }
+  fill_gauss(buf.bias.get(), buf.bias.size(), 77, 0.02f);
+  fill_gauss(buf.residual.get(), buf.residual.size(), 2021, 1.0f);
+  for (int l = 0; l < L; ++l)   // cos/sin over the whole N, theta = 10000 (the reference tests' table)
+    for (int m = 0; m < M; ++m)
+      for (int kp = 0; kp < N / 2; ++kp) {
+        const float freq = 1.0f / std::pow(10000.0f, 2.0f * kp / float(N));
+        const float ang = float(m) * freq;
+        const size_t base = (size_t(l) * M + m) * N;
+        buf.cos_sin.get()[base + 2 * kp] = std::cos(ang);
+        buf.cos_sin.get()[base + 2 * kp + 1] = std::sin(ang);
+      }
+
+  const float* R = buf.row.get();
+  const float* Cv = buf.col.get();
+  const float* Bv = buf.bias.get();
+  const float* CS = buf.cos_sin.get();
+  const bf16* RES = buf.residual.get();
+  auto sMN = cutlass::make_cute_packed_stride(PackedMN{}, make_shape(M, N, L));
+  auto rowv = [&](int l, int m) { return R[size_t(l) * M + m]; };
+  auto rope = [&](int l, int m, int n, float e, float o) {
+    const size_t base = (size_t(l) * M + m) * N;
+    const int ev = n & ~1;
+    const float c = CS[base + ev], s = CS[base + ev + 1];
+    return (n & 1) ? (-e * s + o * c) : (e * c + o * s);
+  };
+  bool ok = false;
+
+  if (p == "k1") {
+    using Kt = xe_fuse::GemmRmsNorm<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M), false,
+                            [&](int l, int m, int n, const float* a) { return a[n] * rowv(l, m); });
+  } else if (p == "k1v2") {
+    using EVT = b::ScaleRowsMerged<TileShape, float>;
+    using Op = b::MakeGemm<EVT, bf16, bf16, bf16, float, float, TileShape>::Gemm;
+    typename b::ColBroadcast<0, TileShape, float>::Arguments sc;
+    sc.ptr_col = buf.row.get(); sc.null_default = 1.f; sc.dCol = {Int<1>{}, Int<0>{}, int64_t(M)};
+    typename EVT::Arguments ea{sc, xe_fuse::XeScaleRowsCompute::Arguments{}};
+    ok = run_case<Op>(P, buf, ea, false, [&](int l, int m, int n, const float* a) { return a[n] * rowv(l, m); });
+  } else if (p == "k2" || p == "k2_compact" || p == "k2_geglu" || p == "moe") {
+    const bool ge = p == "k2_geglu";
+    auto f = [&, ge](int l, int m, int n, const float* a) {
+      const float s = rowv(l, m), g = a[n & ~1] * s, u = a[(n & ~1) + 1] * s;
+      return (ge ? gelu(g) : silu(g)) * u;
+    };
+    if (ge) {
+      using Kt = xe_fuse::GemmRmsNormSwiGLU<bf16, bf16, bf16, float, float, float, TileShape, xe_fuse::GeGLUFn>;
+      ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M), false, f);
+    } else if (p == "moe") {
+      using Kt = xe_fuse::MoEExpertSwiGLU<>;
+      ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M), false, f);
+    } else {
+      using Kt = xe_fuse::GemmRmsNormSwiGLU<>;
+      ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M), false, f, p == "k2_compact");
+    }
+  } else if (p == "k2v2") {
+    using EVT = b::SwiGLUScaled<TileShape, float>;
+    using Op = b::MakeGemm<EVT, bf16, bf16, bf16, float, float, TileShape>::Gemm;
+    typename b::ColBroadcast<0, TileShape, float>::Arguments sc;
+    sc.ptr_col = buf.row.get(); sc.null_default = 1.f; sc.dCol = {Int<1>{}, Int<0>{}, int64_t(M)};
+    typename EVT::Arguments ea{sc, xe_fuse::XeScaleRowsSwiGLUCompute::Arguments{}};
+    ok = run_case<Op>(P, buf, ea, false, [&](int l, int m, int n, const float* a) {
+      const float s = rowv(l, m);
+      return silu(a[n & ~1] * s) * (a[(n & ~1) + 1] * s);
+    });
+  } else if (p == "k8") {
+    using Kt = xe_fuse::GemmSwiGLU<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(), false,
+                            [&](int, int, int n, const float* a) { return silu(a[n & ~1]) * a[(n & ~1) + 1]; });
+  } else if (p == "k3") {
+    using Kt = xe_fuse::GemmRoPE<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.cos_sin.get(), sMN), false,
+                            [&](int l, int m, int n, const float* a) { return rope(l, m, n, a[n & ~1], a[(n & ~1) + 1]); });
+  } else if (p == "k4") {
+    using Kt = xe_fuse::GemmRmsNormRoPE<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M, buf.cos_sin.get(), sMN), false,
+                            [&](int l, int m, int n, const float* a) {
+                              const float s = rowv(l, m);
+                              return rope(l, m, n, a[n & ~1] * s, a[(n & ~1) + 1] * s);
+                            });
+  } else if (p == "k4v2") {
+    using EVT = b::RoPEScaled<TileShape, float, float>;
+    using Op = b::MakeGemm<EVT, bf16, bf16, bf16, float, float, TileShape>::Gemm;
+    typename b::ColBroadcast<0, TileShape, float>::Arguments sc;
+    sc.ptr_col = buf.row.get(); sc.null_default = 1.f; sc.dCol = {Int<1>{}, Int<0>{}, int64_t(M)};
+    typename b::AuxLoad<float>::Arguments cs;
+    cs.ptr_aux = buf.cos_sin.get(); cs.null_default = 0.f; cs.dAux = sMN;
+    typename EVT::Arguments ea{sc, cs, xe_fuse::XeRoPEScaledCompute::Arguments{}};
+    ok = run_case<Op>(P, buf, ea, false, [&](int l, int m, int n, const float* a) {
+      const float s = rowv(l, m);
+      return rope(l, m, n, a[n & ~1] * s, a[(n & ~1) + 1] * s);
+    });
+  } else if (p == "k0a") {
+    using Kt = xe_fuse::GemmResidualGamma<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.residual.get(), sMN, buf.col.get(), N), false,
+                            [&](int l, int m, int n, const float* a) {
+                              return Cv[size_t(l) * N + n] * (a[n] + float(RES[(size_t(l) * M + m) * N + n]));
+                            });
+  } else if (p == "k0") {
+    using Kt = xe_fuse::GemmDualOutput<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.residual.get(), sMN, buf.col.get(), N, buf.aux.get(), sMN),
+                            false,
+                            [&](int l, int m, int n, const float* a) {
+                              return Cv[size_t(l) * N + n] * (a[n] + float(RES[(size_t(l) * M + m) * N + n]));
+                            },
+                            false, {}, true);
+  } else if (p == "bias_gelu") {
+    using EVT = b::GeLU<b::BiasAdd<TileShape, float>>;
+    using Op = b::MakeGemm<EVT, bf16, bf16, bf16, float, float, TileShape>::Gemm;
+    typename b::RowBroadcast<0, TileShape, float>::Arguments bi;
+    bi.ptr_row = buf.bias.get(); bi.null_default = 0.f; bi.dRow = {Int<0>{}, Int<1>{}, int64_t(N)};
+    typename b::BiasAdd<TileShape, float>::Arguments inner{b::Acc::Arguments{}, bi, b::AddOp<>::Arguments{}};
+    typename EVT::Arguments ea{inner, xe_fuse::XeElementwiseCompute<xe_fuse::GeLUFn>::Arguments{}};
+    ok = run_case<Op>(P, buf, ea, false,
+                      [&](int l, int, int n, const float* a) { return gelu(a[n] + Bv[size_t(l) * N + n]); });
+  } else if (p == "w8a8") {
+    using Kt = xe_fuse::GemmDequantW8A8<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M, buf.col.get(), N), true,
+                            [&](int l, int m, int n, const float* a) { return a[n] * rowv(l, m) * Cv[size_t(l) * N + n]; });
+  } else if (p == "w8a8_biased") {
+    using EVT = b::DequantW8A8Biased<TileShape, float, float, float>;
+    using Op = b::MakeGemm<EVT, int8_t, int8_t, bf16, int32_t, float, TileShape, cutlass::layout::RowMajor,
+                           cutlass::layout::RowMajor, 32, 8>::Gemm;
+    auto deq = xe_fuse::GemmDequantW8A8<>::make_evt_args(buf.row.get(), M, buf.col.get(), N);
+    typename b::RowBroadcast<2, TileShape, float>::Arguments bi;
+    bi.ptr_row = buf.bias.get(); bi.null_default = 0.f; bi.dRow = {Int<0>{}, Int<1>{}, int64_t(N)};
+    typename EVT::Arguments ea{deq, bi, b::AddOp<>::Arguments{}};
+    ok = run_case<Op>(P, buf, ea, true, [&](int l, int m, int n, const float* a) {
+      return a[n] * rowv(l, m) * Cv[size_t(l) * N + n] + Bv[size_t(l) * N + n];
+    });
+  } else if (p == "w8a8_rope") {
+    using Kt = xe_fuse::GemmDequantRoPE<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M, buf.col.get(), N, buf.cos_sin.get(), sMN), true,
+                            [&](int l, int m, int n, const float* a) {
+                              const int ev = n & ~1;
+                              const float s = rowv(l, m);
+                              return rope(l, m, n, a[ev] * s * Cv[size_t(l) * N + ev], a[ev + 1] * s * Cv[size_t(l) * N + ev + 1]);
+                            });
+  } else if (p == "w8a8_swiglu") {
+    using Kt = xe_fuse::GemmDequantSwiGLU<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M, buf.col.get(), N), true,
+                            [&](int l, int m, int n, const float* a) {
+                              const int ev = n & ~1;
+                              const float s = rowv(l, m);
+                              return silu(a[ev] * s * Cv[size_t(l) * N + ev]) * (a[ev + 1] * s * Cv[size_t(l) * N + ev + 1]);
+                            });
+  } else if (p == "unsupported") {
+    // a tree outside the flat program must be refused, not run: gamma[n] applied after GeLU
+    using EVT = b::ScaleCols<b::GeLU<b::Acc>, TileShape, float>;
+    using Op = b::MakeGemm<EVT, bf16, bf16, bf16, float, float, TileShape>::Gemm;
+    typename b::RowBroadcast<0, TileShape, float>::Arguments g;
+    g.ptr_row = buf.col.get(); g.null_default = 1.f; g.dRow = {Int<0>{}, Int<1>{}, int64_t(N)};
+    typename b::GeLU<b::Acc>::Arguments inner{b::Acc::Arguments{}, xe_fuse::XeElementwiseCompute<xe_fuse::GeLUFn>::Arguments{}};
+    typename EVT::Arguments ea{g, inner, b::MulOp<>::Arguments{}};
+    using Kernel = typename Op::GemmKernel;
+    auto sA = cutlass::make_cute_packed_stride(typename Kernel::StrideA{}, make_shape(M, K, L));
+    auto sB = cutlass::make_cute_packed_stride(typename Kernel::StrideB{}, make_shape(N, K, L));
+    typename Kernel::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, L},
+                                    {buf.A.get(), sA, buf.B.get(), sB}, {ea, nullptr, sMN, buf.D.get(), sMN}, {}};
+    const bool refused = Op::can_implement(args) == cutlass::Status::kErrorNotSupported;
+    std::cout << "Disposition: " << (refused ? "Passed" : "Failed") << " (refusal expected)" << std::endl;
+    ok = refused;
+  } else {
+    std::cerr << "unknown preset " << p << std::endl;
+    return 2;
+  }
+  return ok ? 0 : 1;
+}

@@ -65,6 +65,7 @@ EXPORTS = [
     "xf_sa_scale_rows", "xf_sa_scale_cols", "xf_sa_add_residual", "xf_sa_residual_gamma",
     "xf_sa_swiglu", "xf_sa_geglu", "xf_sa_rope", "xf_sa_rope_scaled", "xf_sa_unary",
     "xf_sa_bias_add", "xf_sa_dequant_w8a8", "xf_compute_rstd", "xf_compute_rstd_and_quantize",
+    "xf_harness_fill_uniform", "xf_harness_ref_gemm", "xf_harness_compare",
 ]
 
 _lib = None

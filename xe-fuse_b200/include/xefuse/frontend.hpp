@@ -1,0 +1,775 @@
+// Header-only C++17 front end of xefuse_b200.
+//
+// It re-creates, in this project's own code, the vocabulary the callers of Xe-Fuse's builder API
+// spell -- cutlass::Status, cutlass::bfloat16_t, the epilogue visitor-tree node types with their
+// `Arguments`, CollectiveBuilder / GemmUniversal / GemmUniversalAdapter -- but no template here
+// instantiates device code.  An EVT type together with its run-time Arguments tree is LOWERED to
+// the flat epilogue program of include/xefuse_b200.h (xf_epilogue_desc) and handed to the
+// pre-compiled sm_100a kernels through the C ABI.  A tree that does not fit the flat program makes
+// can_implement()/initialize() return Status::kErrorNotSupported; nothing falls back to a CPU.
+//
+// Reference surface mirrored (paths inside IntelLabs/Xe-Fuse):
+//   include/xe-fuse/builder/epilogue_builder.hpp:58-382   aliases and MakeGemm
+//   tests/test_k1.cpp:54-103                               how a caller drives a Gemm object
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <tuple>
+#include <type_traits>
+
+#include "cute/tensor.hpp"
+#include "xefuse_b200.h"
+
+// ------------------------------------------------------------------------------------------------
+// cutlass:: basic vocabulary
+// ------------------------------------------------------------------------------------------------
+#ifndef CUTLASS_HOST_DEVICE
+#define CUTLASS_HOST_DEVICE inline
+#define CUTLASS_DEVICE inline
+#define CUTLASS_PRAGMA_UNROLL
+#endif
+
+namespace cutlass {
+
+enum class Status {
+  kSuccess = XF_SUCCESS,
+  kErrorMisalignedOperand = XF_ERR_MISALIGNED_OPERAND,
+  kErrorInvalidDataType = XF_ERR_INVALID_DATA_TYPE,
+  kErrorInvalidLayout = XF_ERR_INVALID_LAYOUT,
+  kErrorInvalidProblem = XF_ERR_INVALID_PROBLEM,
+  kErrorNotSupported = XF_ERR_NOT_SUPPORTED,
+  kErrorWorkspaceNull = XF_ERR_WORKSPACE_NULL,
+  kErrorInternal = XF_ERR_INTERNAL,
+  kErrorArchMismatch = XF_ERR_ARCH_MISMATCH,
+  kErrorInsufficientDriver = XF_ERR_INSUFFICIENT_DRIVER,
+  kErrorMemoryAllocation = XF_ERR_MEMORY_ALLOCATION,
+  kInvalid = XF_INVALID
+};
+
+inline const char* cutlassGetStatusString(Status s) { return xf_status_string(static_cast<xf_status>(s)); }
+
+// bfloat16 value type for host code: storage is the 16-bit pattern, arithmetic goes through float,
+// float -> bf16 is round-to-nearest-even.
+struct alignas(2) bfloat16_t {
+  uint16_t storage = 0;
+  bfloat16_t() = default;
+  bfloat16_t(float f) { storage = from_float(f); }
+  bfloat16_t(double f) { storage = from_float(static_cast<float>(f)); }
+  bfloat16_t(int i) { storage = from_float(static_cast<float>(i)); }
+  static bfloat16_t bitcast(uint16_t bits) { bfloat16_t r; r.storage = bits; return r; }
+  operator float() const {
+    uint32_t u = static_cast<uint32_t>(storage) << 16;
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+  }
+  static uint16_t from_float(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((u >> 16) | 0x0040u);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return static_cast<uint16_t>(u >> 16);
+  }
+};
+inline bfloat16_t operator+(bfloat16_t a, bfloat16_t b) { return bfloat16_t(float(a) + float(b)); }
+inline bfloat16_t operator-(bfloat16_t a, bfloat16_t b) { return bfloat16_t(float(a) - float(b)); }
+inline bfloat16_t operator*(bfloat16_t a, bfloat16_t b) { return bfloat16_t(float(a) * float(b)); }
+inline bfloat16_t operator/(bfloat16_t a, bfloat16_t b) { return bfloat16_t(float(a) / float(b)); }
+inline bfloat16_t operator-(bfloat16_t a) { return bfloat16_t(-float(a)); }
+inline bool operator==(bfloat16_t a, bfloat16_t b) { return float(a) == float(b); }
+inline bool operator!=(bfloat16_t a, bfloat16_t b) { return float(a) != float(b); }
+inline bool operator<(bfloat16_t a, bfloat16_t b) { return float(a) < float(b); }
+inline bool operator>(bfloat16_t a, bfloat16_t b) { return float(a) > float(b); }
+
+template <class T> struct sizeof_bits { static constexpr int value = int(sizeof(T) * 8); };
+template <class T> inline constexpr int sizeof_bits_v = sizeof_bits<T>::value;
+
+enum class FloatRoundStyle { round_indeterminate, round_toward_zero, round_to_nearest, round_to_nearest_satfinite };
+enum class ComplexTransform { kNone, kConjugate };
+
+template <class T> struct multiplies { T operator()(T a, T b) const { return a * b; } };
+template <class T> struct plus { T operator()(T a, T b) const { return a + b; } };
+template <class T> struct minus { T operator()(T a, T b) const { return a - b; } };
+
+struct MatrixCoord {
+  int r = 0, c = 0;
+  MatrixCoord() = default;
+  MatrixCoord(int row, int col) : r(row), c(col) {}
+  int row() const { return r; }
+  int column() const { return c; }
+};
+
+namespace layout {
+struct RowMajor {
+  int64_t ld = 0;
+  RowMajor() = default;
+  explicit RowMajor(int64_t l) : ld(l) {}
+  static RowMajor packed(MatrixCoord const& extent) { return RowMajor(extent.column()); }
+  int64_t stride(int = 0) const { return ld; }
+};
+struct ColumnMajor {
+  int64_t ld = 0;
+  ColumnMajor() = default;
+  explicit ColumnMajor(int64_t l) : ld(l) {}
+  static ColumnMajor packed(MatrixCoord const& extent) { return ColumnMajor(extent.row()); }
+  int64_t stride(int = 0) const { return ld; }
+};
+}  // namespace layout
+
+template <class Element_, class Layout_>
+class TensorRef {
+ public:
+  using Element = Element_;
+  using Layout = Layout_;
+  TensorRef() = default;
+  TensorRef(Element* p, Layout l) : ptr_(p), layout_(l) {}
+  Element* data() const { return ptr_; }
+  Layout const& layout() const { return layout_; }
+  int64_t stride(int i = 0) const { return layout_.stride(i); }
+ private:
+  Element* ptr_ = nullptr;
+  Layout layout_{};
+};
+
+namespace gemm {
+enum class GemmUniversalMode { kGemm, kGemmSplitKParallel, kBatched, kArray, kGrouped, kInvalid };
+struct GemmCoord {
+  int m_ = 0, n_ = 0, k_ = 0;
+  GemmCoord() = default;
+  GemmCoord(int m, int n, int k) : m_(m), n_(n), k_(k) {}
+  int m() const { return m_; }
+  int n() const { return n_; }
+  int k() const { return k_; }
+};
+}  // namespace gemm
+
+namespace arch {
+struct Xe20 {};            // architecture tag callers pass; this build always targets sm_100a
+struct IntelXe {};
+struct Sm100 {};
+struct OpClassTensorOp {};
+struct OpClassSimt {};
+}  // namespace arch
+
+struct KernelHardwareInfo {
+  int device_id = 0;
+  int sm_count = 0;
+  static int query_device_multiprocessor_count(int device_id = 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device_id) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    return n;
+  }
+};
+
+}  // namespace cutlass
+
+// ------------------------------------------------------------------------------------------------
+// lowering machinery
+// ------------------------------------------------------------------------------------------------
+namespace xefuse {
+
+template <class T> struct DType;
+template <> struct DType<float> { static constexpr int value = XF_DT_F32; };
+template <> struct DType<cutlass::bfloat16_t> { static constexpr int value = XF_DT_BF16; };
+template <> struct DType<int8_t> { static constexpr int value = XF_DT_S8; };
+template <> struct DType<int32_t> { static constexpr int value = XF_DT_S32; };
+
+// Steps of the flat epilogue program, in order.
+enum Stage : int { kAcc = 0, kResidual, kAuxStore, kRow, kCol, kBias, kUnary, kPair };
+
+// What a subtree evaluates to while lowering.
+struct Val {
+  enum Kind { kInvalid, kValue, kRowVec, kColVec, kMat } kind = kInvalid;
+  int stage = kAcc;           // kValue: last step of the flat program this value has been through
+  const void* ptr = nullptr;  // leaves
+  int dtype = XF_DT_F32;
+  float null_default = 0.f;
+  int64_t ld = 0, batch = 0;
+};
+
+struct Ctx {
+  xf_epilogue_desc epi;
+  bool ok = true;
+  const char* why = "";
+  int acc_uses = 0;
+  bool acc_bound = false;     // inside a split tree's output tree, Acc names the input tree's value
+  Val acc_binding;
+  Ctx() { std::memset(&epi, 0, sizeof(epi)); }
+  Val fail(const char* msg) {
+    if (ok) why = msg;
+    ok = false;
+    return Val{};
+  }
+};
+
+inline Val value_at(int stage) { Val v; v.kind = Val::kValue; v.stage = stage; return v; }
+
+inline xf_vec to_vec(Val const& v) {
+  xf_vec r;
+  std::memset(&r, 0, sizeof(r));
+  r.ptr = v.ptr; r.dtype = v.dtype; r.enabled = 1; r.batch_stride = v.batch; r.null_default = v.null_default;
+  return r;
+}
+inline xf_mat to_mat(Val const& v) {
+  xf_mat r;
+  std::memset(&r, 0, sizeof(r));
+  r.ptr = v.ptr; r.dtype = v.dtype; r.enabled = 1; r.ld = v.ld; r.batch_stride = v.batch;
+  return r;
+}
+
+inline Val lower_mul(Val a, Val b, Ctx& c) {
+  if (a.kind != Val::kValue) std::swap(a, b);
+  if (a.kind != Val::kValue) return c.fail("a product needs the running value as one operand");
+  if (b.kind == Val::kRowVec) {
+    // per-row scale: before col/bias in the flat order; after the column scale it still commutes
+    if (c.epi.row_scale.enabled) return c.fail("two per-row scales in one tree");
+    if (a.stage < kRow || (a.stage == kCol && !c.epi.bias.enabled)) {
+      c.epi.row_scale = to_vec(b);
+      a.stage = a.stage < kRow ? int(kRow) : a.stage;
+      return a;
+    }
+    return c.fail("per-row scale after bias/activation does not fit the flat epilogue order");
+  }
+  if (b.kind == Val::kColVec) {
+    if (c.epi.col_scale.enabled) return c.fail("two per-column scales in one tree");
+    if (a.stage < kCol) {
+      c.epi.col_scale = to_vec(b);
+      a.stage = kCol;
+      return a;
+    }
+    return c.fail("per-column scale after bias/activation does not fit the flat epilogue order");
+  }
+  return c.fail("product with a full tensor operand is not supported");
+}
+
+inline Val lower_add(Val a, Val b, Ctx& c) {
+  if (a.kind != Val::kValue) std::swap(a, b);
+  if (a.kind != Val::kValue) return c.fail("a sum needs the running value as one operand");
+  if (b.kind == Val::kMat) {
+    if (a.stage != kAcc || c.epi.residual.enabled)
+      return c.fail("a full-tensor addend is only supported directly on the accumulator");
+    c.epi.residual = to_mat(b);
+    a.stage = kResidual;
+    return a;
+  }
+  if (b.kind == Val::kColVec) {
+    if (a.stage >= kBias || c.epi.bias.enabled) return c.fail("per-column addend after the bias step");
+    c.epi.bias = to_vec(b);
+    a.stage = kBias;
+    return a;
+  }
+  return c.fail("per-row addend is not supported");
+}
+
+inline Val lower_unary(Val a, int op, Ctx& c) {
+  if (a.kind != Val::kValue || a.stage >= kUnary) return c.fail("activation after another activation/pair op");
+  c.epi.unary = op;
+  a.stage = kUnary;
+  return a;
+}
+
+inline Val lower_pair(Val a, int op, Ctx& c) {
+  if (a.kind != Val::kValue || a.stage >= kPair) return c.fail("two pair ops in one tree");
+  c.epi.pair = op;
+  a.stage = kPair;
+  return a;
+}
+
+inline Val lower_rope(Val a, Val cs, Ctx& c) {
+  if (cs.kind != Val::kMat) return c.fail("RoPE needs a cos_sin AuxLoad child");
+  if (cs.dtype != XF_DT_F32) return c.fail("cos_sin must be fp32");
+  Val r = lower_pair(a, XF_PAIR_ROPE, c);
+  c.epi.cos_sin = to_mat(cs);
+  return r;
+}
+
+// Node -> lowering rule; specialised below each node type.
+template <class Node, class Enable = void>
+struct Lower {
+  template <class Args>
+  static Val apply(Args const&, Ctx& c) { return c.fail("epilogue node not supported by xefuse_b200"); }
+};
+
+template <class Node, class Args>
+inline Val lower(Args const& a, Ctx& c) { return Lower<Node>::apply(a, c); }
+
+// Extensions beyond the reference API, set on the Gemm object before initialize().
+struct Extensions {
+  bool compact_pair_output = false;  // SwiGLU/GeGLU write [M, N/2] (one value per pair)
+  int cos_sin_period = 0;            // RoPE table is [M, period]; column n reads n % period
+  int flags = 0;                     // XF_FLAG_* passed through
+};
+
+}  // namespace xefuse
+
+// ------------------------------------------------------------------------------------------------
+// epilogue visitor-tree node types (own definitions of the names the reference's aliases map to)
+// ------------------------------------------------------------------------------------------------
+namespace cutlass::epilogue::fusion {
+
+struct XeAccFetch { struct Arguments {}; };
+using Sm90AccFetch = XeAccFetch;
+
+template <int Stages, class TileShape, class Element, class ElementCompute = float,
+          class StrideMNL = cute::Stride<cute::_1, cute::_0, int64_t>, int Alignment = 4>
+struct XeColBroadcast {
+  struct Arguments {
+    Element const* ptr_col = nullptr;
+    Element null_default = Element(0);
+    StrideMNL dCol = {};
+  };
+};
+
+template <int Stages, class TileShape, class Element, class ElementCompute = float,
+          class StrideMNL = cute::Stride<cute::_0, cute::_1, int64_t>, int Alignment = 4>
+struct XeRowBroadcast {
+  struct Arguments {
+    Element const* ptr_row = nullptr;
+    Element null_default = Element(0);
+    StrideMNL dRow = {};
+  };
+};
+
+template <class Element, class StrideMNL = cute::Stride<int64_t, cute::_1, int64_t>, class CopyOp = void,
+          int Alignment = 4, bool EnableNullptr = true, bool UseBlock2D = true>
+struct XeAuxLoad {
+  struct Arguments {
+    Element const* ptr_aux = nullptr;
+    Element null_default = Element(0);
+    StrideMNL dAux = {};
+  };
+};
+
+template <class Element, class StrideMNL = cute::Stride<int64_t, cute::_1, int64_t>, class CopyOp = void,
+          int Alignment = 4, bool EnableNullptr = true, bool UseBlock2D = false>
+struct XeAuxStore {
+  struct Arguments {
+    Element* ptr_aux = nullptr;
+    Element null_default = Element(0);
+    StrideMNL dAux = {};
+  };
+};
+
+template <template <class> class ComputeFn, class ElementOutput, class ElementCompute,
+          FloatRoundStyle Round = FloatRoundStyle::round_to_nearest>
+struct XeCompute { struct Arguments {}; };
+
+// Tree node: children first, then the node op (brace-init order {child0, child1, ..., op}).
+template <class NodeOp, class... ChildOps>
+struct XeEVT {
+  using Arguments = std::tuple<typename ChildOps::Arguments..., typename NodeOp::Arguments>;
+};
+template <class NodeOp, class... ChildOps> using Sm90EVT = XeEVT<NodeOp, ChildOps...>;
+
+// Evaluate InputTree once; every AuxOutTree and the OutputTree see its value as their `Acc`.
+// Arguments order {input, aux..., output}.
+template <class InputTree, class OutputTree, class... AuxOutTrees>
+struct Sm90SplitTreeVisitor {
+  using Arguments = std::tuple<typename InputTree::Arguments, typename AuxOutTrees::Arguments...,
+                               typename OutputTree::Arguments>;
+};
+
+// Default fusion when a CollectiveBuilder is given no EVT: D = alpha * acc + beta * C.
+template <class ElementOutput, class ElementCompute = float>
+struct LinearCombination {
+  struct Arguments {
+    ElementCompute alpha = ElementCompute(1);
+    ElementCompute beta = ElementCompute(0);
+    ElementCompute const* alpha_ptr = nullptr;
+    ElementCompute const* beta_ptr = nullptr;
+  };
+};
+
+}  // namespace cutlass::epilogue::fusion
+
+namespace xefuse {
+namespace fus = cutlass::epilogue::fusion;
+
+template <>
+struct Lower<fus::XeAccFetch> {
+  template <class Args>
+  static Val apply(Args const&, Ctx& c) {
+    if (c.acc_bound) return c.acc_binding;
+    if (++c.acc_uses > 1) return c.fail("the accumulator is fetched twice in one tree");
+    return value_at(kAcc);
+  }
+};
+
+template <int S, class TS, class E, class EC, class St, int Al>
+struct Lower<fus::XeColBroadcast<S, TS, E, EC, St, Al>> {
+  template <class Args>
+  static Val apply(Args const& a, Ctx&) {
+    Val v; v.kind = Val::kRowVec;  // "column broadcast" = one value per ROW, replicated along N
+    v.ptr = a.ptr_col; v.dtype = DType<E>::value; v.null_default = float(a.null_default);
+    v.batch = int64_t(std::get<2>(a.dCol));
+    return v;
+  }
+};
+
+template <int S, class TS, class E, class EC, class St, int Al>
+struct Lower<fus::XeRowBroadcast<S, TS, E, EC, St, Al>> {
+  template <class Args>
+  static Val apply(Args const& a, Ctx&) {
+    Val v; v.kind = Val::kColVec;
+    v.ptr = a.ptr_row; v.dtype = DType<E>::value; v.null_default = float(a.null_default);
+    v.batch = int64_t(std::get<2>(a.dRow));
+    return v;
+  }
+};
+
+template <class E, class St, class Cp, int Al, bool En, bool B2>
+struct Lower<fus::XeAuxLoad<E, St, Cp, Al, En, B2>> {
+  template <class Args>
+  static Val apply(Args const& a, Ctx& c) {
+    if (a.ptr_aux == nullptr) return c.fail("AuxLoad with a null pointer");
+    Val v; v.kind = Val::kMat;
+    v.ptr = a.ptr_aux; v.dtype = DType<E>::value; v.null_default = float(a.null_default);
+    v.ld = int64_t(std::get<0>(a.dAux)); v.batch = int64_t(std::get<2>(a.dAux));
+    return v;
+  }
+};
+
+// Mul / Add nodes
+template <class EO, class EC, cutlass::FloatRoundStyle R, class A, class B>
+struct Lower<fus::XeEVT<fus::XeCompute<cutlass::multiplies, EO, EC, R>, A, B>> {
+  template <class Args>
+  static Val apply(Args const& t, Ctx& c) {
+    Val a = lower<A>(std::get<0>(t), c);
+    Val b = lower<B>(std::get<1>(t), c);
+    if (!c.ok) return Val{};
+    return lower_mul(a, b, c);
+  }
+};
+template <class EO, class EC, cutlass::FloatRoundStyle R, class A, class B>
+struct Lower<fus::XeEVT<fus::XeCompute<cutlass::plus, EO, EC, R>, A, B>> {
+  template <class Args>
+  static Val apply(Args const& t, Ctx& c) {
+    Val a = lower<A>(std::get<0>(t), c);
+    Val b = lower<B>(std::get<1>(t), c);
+    if (!c.ok) return Val{};
+    return lower_add(a, b, c);
+  }
+};
+
+// AuxStore of a value: EVT<AuxStore, X>
+template <class E, class St, class Cp, int Al, bool En, bool B2, class X>
+struct Lower<fus::XeEVT<fus::XeAuxStore<E, St, Cp, Al, En, B2>, X>> {
+  template <class Args>
+  static Val apply(Args const& t, Ctx& c) {
+    Val v = lower<X>(std::get<0>(t), c);
+    if (!c.ok) return Val{};
+    auto const& s = std::get<1>(t);
+    if (v.kind != Val::kValue || v.stage > kResidual) return c.fail("aux store after the scale steps");
+    if (DType<E>::value != XF_DT_BF16) return c.fail("aux store writes bf16 only");
+    if (s.ptr_aux == nullptr) return v;  // null pointer: store disabled
+    std::memset(&c.epi.aux_store, 0, sizeof(xf_mat));
+    c.epi.aux_store.ptr = s.ptr_aux; c.epi.aux_store.dtype = XF_DT_BF16; c.epi.aux_store.enabled = 1;
+    c.epi.aux_store.ld = int64_t(std::get<0>(s.dAux)); c.epi.aux_store.batch_stride = int64_t(std::get<2>(s.dAux));
+    v.stage = kAuxStore;
+    return v;
+  }
+};
+
+template <class In, class Out, class... Aux>
+struct Lower<fus::Sm90SplitTreeVisitor<In, Out, Aux...>> {
+  template <class Args, std::size_t... I>
+  static void lower_aux(Args const& t, Ctx& c, std::index_sequence<I...>) {
+    (void)std::initializer_list<int>{(c.acc_binding = lower<Aux>(std::get<1 + I>(t), c), 0)...};
+  }
+  template <class Args>
+  static Val apply(Args const& t, Ctx& c) {
+    if (c.acc_bound) return c.fail("nested split trees are not supported");
+    Val in = lower<In>(std::get<0>(t), c);
+    if (!c.ok) return Val{};
+    c.acc_bound = true;
+    c.acc_binding = in;
+    lower_aux(t, c, std::index_sequence_for<Aux...>{});
+    if (!c.ok) return Val{};
+    Val out = lower<Out>(std::get<sizeof...(Aux) + 1>(t), c);
+    c.acc_bound = false;
+    return out;
+  }
+};
+
+template <class EO, class EC>
+struct Lower<fus::LinearCombination<EO, EC>> {
+  template <class Args>
+  static Val apply(Args const& a, Ctx& c) {
+    if (a.alpha_ptr || a.beta_ptr) return c.fail("alpha/beta device pointers are not supported");
+    if (float(a.beta) != 0.f) return c.fail("beta != 0 (source tensor C) is not supported");
+    Val v = value_at(kAcc);
+    if (float(a.alpha) != 1.f) {
+      Val s; s.kind = Val::kRowVec; s.ptr = nullptr; s.dtype = XF_DT_F32; s.null_default = float(a.alpha);
+      v = lower_mul(v, s, c);
+    }
+    return v;
+  }
+};
+
+}  // namespace xefuse
+
+// ------------------------------------------------------------------------------------------------
+// collectives, kernel, adapter
+// ------------------------------------------------------------------------------------------------
+namespace cutlass::epilogue::collective {
+struct EpilogueTileAuto {};
+struct EpilogueScheduleAuto {};
+struct NoSmemWarpSpecialized {};
+}  // namespace cutlass::epilogue::collective
+
+namespace cutlass::gemm::collective {
+struct StageCountAuto {};
+struct KernelScheduleAuto {};
+template <int N> struct StageCount { static constexpr int value = N; };
+}  // namespace cutlass::gemm::collective
+
+namespace xefuse {
+
+template <class TileShape_, class ElementAcc_, class ElementCompute_, class ElementC_, class StrideC_,
+          class ElementD_, class StrideD_, class FusionOp_>
+struct EpilogueOp {
+  using TileShape = TileShape_;
+  using ElementAccumulator = ElementAcc_;
+  using ElementCompute = ElementCompute_;
+  using ElementC = ElementC_;
+  using ElementD = ElementD_;
+  using StrideC = StrideC_;
+  using StrideD = StrideD_;
+  using FusionCallbacks = FusionOp_;
+  struct Arguments {
+    typename FusionOp_::Arguments thread{};
+    ElementC const* ptr_C = nullptr;
+    StrideC dC{};
+    ElementD* ptr_D = nullptr;
+    StrideD dD{};
+  };
+};
+
+template <class L> struct StrideOfA;   // A is (M,K,L)
+template <> struct StrideOfA<cutlass::layout::RowMajor> { using type = cute::Stride<int64_t, cute::_1, int64_t>; };
+template <class L> struct StrideOfB;   // B is (N,K,L); row-major [K,N] storage => N has unit stride
+template <> struct StrideOfB<cutlass::layout::RowMajor> { using type = cute::Stride<cute::_1, int64_t, int64_t>; };
+
+template <class ElementA_, class LayoutA_, class ElementB_, class LayoutB_, class ElementAcc_, class TileShape_>
+struct MainloopOp {
+  using ElementA = ElementA_;
+  using ElementB = ElementB_;
+  using LayoutA = LayoutA_;
+  using LayoutB = LayoutB_;
+  using ElementAccumulator = ElementAcc_;
+  using TileShape = TileShape_;
+  using StrideA = typename StrideOfA<LayoutA_>::type;
+  using StrideB = typename StrideOfB<LayoutB_>::type;
+  struct Arguments {
+    ElementA const* ptr_A = nullptr;
+    StrideA dA{};
+    ElementB const* ptr_B = nullptr;
+    StrideB dB{};
+  };
+};
+
+}  // namespace xefuse
+
+namespace cutlass::epilogue::collective {
+template <class ArchTag, class OpClass, class TileShape, class ClusterShape, class EpilogueTile,
+          class ElementAcc, class ElementCompute, class ElementC, class StrideC, int AlignC,
+          class ElementD, class StrideD, int AlignD, class Schedule,
+          class FusionOp = cutlass::epilogue::fusion::LinearCombination<ElementD, ElementCompute>>
+struct CollectiveBuilder {
+  using CollectiveOp = xefuse::EpilogueOp<TileShape, ElementAcc, ElementCompute, ElementC, StrideC,
+                                          ElementD, StrideD, FusionOp>;
+};
+}  // namespace cutlass::epilogue::collective
+
+namespace cutlass::gemm::collective {
+template <class ArchTag, class OpClass, class ElementA, class LayoutA, int AlignA, class ElementB,
+          class LayoutB, int AlignB, class ElementAcc, class TileShape, class ClusterShape,
+          class StageCountType, class Schedule>
+struct CollectiveBuilder {
+  using CollectiveOp = xefuse::MainloopOp<ElementA, LayoutA, ElementB, LayoutB, ElementAcc, TileShape>;
+};
+}  // namespace cutlass::gemm::collective
+
+namespace cutlass::gemm::kernel {
+
+template <class ProblemShape_, class CollectiveMainloop_, class CollectiveEpilogue_, class TileScheduler_ = void>
+struct GemmUniversal {
+  using ProblemShape = ProblemShape_;
+  using CollectiveMainloop = CollectiveMainloop_;
+  using CollectiveEpilogue = CollectiveEpilogue_;
+  using ElementA = typename CollectiveMainloop::ElementA;
+  using ElementB = typename CollectiveMainloop::ElementB;
+  using ElementC = typename CollectiveEpilogue::ElementC;
+  using ElementD = typename CollectiveEpilogue::ElementD;
+  using ElementAccumulator = typename CollectiveMainloop::ElementAccumulator;
+  using StrideA = typename CollectiveMainloop::StrideA;
+  using StrideB = typename CollectiveMainloop::StrideB;
+  using StrideC = typename CollectiveEpilogue::StrideC;
+  using StrideD = typename CollectiveEpilogue::StrideD;
+  using TileShape = typename CollectiveMainloop::TileShape;
+  using MainloopArguments = typename CollectiveMainloop::Arguments;
+  using EpilogueArguments = typename CollectiveEpilogue::Arguments;
+  struct Arguments {
+    GemmUniversalMode mode = GemmUniversalMode::kGemm;
+    ProblemShape problem_shape{};
+    MainloopArguments mainloop{};
+    EpilogueArguments epilogue{};
+    KernelHardwareInfo hw_info{};
+  };
+};
+
+}  // namespace cutlass::gemm::kernel
+
+namespace cutlass::gemm::device {
+
+// The object callers hold: can_implement / get_workspace_size / initialize / run, as
+// GemmUniversalAdapter in the reference's harnesses (tests/test_k1.cpp:95-102).
+template <class GemmKernel_>
+class GemmUniversalAdapter {
+ public:
+  using GemmKernel = GemmKernel_;
+  using Arguments = typename GemmKernel::Arguments;
+  using ElementA = typename GemmKernel::ElementA;
+  using ElementB = typename GemmKernel::ElementB;
+  using ElementD = typename GemmKernel::ElementD;
+  using Fusion = typename GemmKernel::CollectiveEpilogue::FusionCallbacks;
+
+  GemmUniversalAdapter() = default;
+  GemmUniversalAdapter(GemmUniversalAdapter const&) = delete;
+  GemmUniversalAdapter& operator=(GemmUniversalAdapter const&) = delete;
+  ~GemmUniversalAdapter() { release(); }
+
+  void set_extensions(xefuse::Extensions const& e) { ext_ = e; }
+  const char* kernel_name() const { return plan_ ? xf_gemm_plan_kernel_name(plan_) : ""; }
+  static const char* last_error() { return xf_last_error_string(); }
+
+  // Lowers the reference-style arguments to the C ABI descriptor.
+  static Status lower(Arguments const& a, xefuse::Extensions const& ext, xf_gemm_desc& d) {
+    static_assert(std::is_same<ElementA, ElementB>::value, "A and B must have the same element type");
+    std::memset(&d, 0, sizeof(d));
+    if (a.mode != GemmUniversalMode::kGemm && a.mode != GemmUniversalMode::kBatched)
+      return Status::kErrorNotSupported;
+    d.dtype_ab = xefuse::DType<ElementA>::value;
+    d.dtype_d = xefuse::DType<ElementD>::value;
+    d.M = int(std::get<0>(a.problem_shape));
+    d.N = int(std::get<1>(a.problem_shape));
+    d.K = int(std::get<2>(a.problem_shape));
+    d.L = int(std::get<3>(a.problem_shape));
+    d.A = a.mainloop.ptr_A;
+    d.lda = int64_t(std::get<0>(a.mainloop.dA));
+    d.batch_a = int64_t(std::get<2>(a.mainloop.dA));
+    d.B = a.mainloop.ptr_B;
+    d.ldb = int64_t(std::get<1>(a.mainloop.dB));
+    d.batch_b = int64_t(std::get<2>(a.mainloop.dB));
+    d.D = a.epilogue.ptr_D;
+    d.ldd = int64_t(std::get<0>(a.epilogue.dD));
+    d.batch_d = int64_t(std::get<2>(a.epilogue.dD));
+    using TS = typename GemmKernel::TileShape;
+    d.tile_m = int(std::tuple_element_t<0, TS>::value);
+    d.tile_n = int(std::tuple_element_t<1, TS>::value);
+    d.tile_k = int(std::tuple_element_t<2, TS>::value);
+    d.flags = ext.flags;
+    if (a.epilogue.ptr_C != nullptr) return Status::kErrorNotSupported;  // no source tensor path
+    xefuse::Ctx c;
+    xefuse::Val v = xefuse::lower<Fusion>(a.epilogue.thread, c);
+    if (!c.ok || v.kind != xefuse::Val::kValue) {
+      last_lowering_error() = c.ok ? "the tree does not produce a value" : c.why;
+      return Status::kErrorNotSupported;
+    }
+    d.epi = c.epi;
+    d.epi.cos_sin_period = ext.cos_sin_period;
+    d.epi.out_layout = ext.compact_pair_output ? XF_OUT_COMPACT : XF_OUT_FULL;
+    return Status::kSuccess;
+  }
+  static const char*& last_lowering_error() {
+    static thread_local const char* e = "";
+    return e;
+  }
+
+  static Status can_implement(Arguments const& a) { return can_implement(a, xefuse::Extensions{}); }
+  static Status can_implement(Arguments const& a, xefuse::Extensions const& ext) {
+    xf_gemm_desc d;
+    Status s = lower(a, ext, d);
+    if (s != Status::kSuccess) return s;
+    return Status(xf_gemm_can_implement(&d));
+  }
+
+  static size_t get_workspace_size(Arguments const& a) {
+    xf_gemm_desc d;
+    size_t n = 0;
+    if (lower(a, xefuse::Extensions{}, d) != Status::kSuccess) return 16;
+    xf_gemm_workspace_size(&d, &n);
+    return n;
+  }
+
+  Status initialize(Arguments const& a, void* workspace = nullptr, cudaStream_t stream = nullptr) {
+    xf_gemm_desc d;
+    Status s = lower(a, ext_, d);
+    if (s != Status::kSuccess) return s;
+    release();
+    s = Status(xf_gemm_plan_create(&d, workspace, &plan_));
+    if (s != Status::kSuccess) return s;
+    make_resident(d, stream);
+    return Status::kSuccess;
+  }
+
+  Status update(Arguments const& a, void* workspace = nullptr) { return initialize(a, workspace); }
+
+  Status run(cudaStream_t stream = nullptr) {
+    if (!plan_) return Status::kErrorInternal;
+    return Status(xf_gemm_run(plan_, stream));
+  }
+  Status run(Arguments const& a, void* workspace = nullptr, cudaStream_t stream = nullptr) {
+    Status s = initialize(a, workspace, stream);
+    return s == Status::kSuccess ? run(stream) : s;
+  }
+  Status operator()(cudaStream_t stream = nullptr) { return run(stream); }
+  Status operator()(Arguments const& a, void* workspace = nullptr, cudaStream_t stream = nullptr) {
+    return run(a, workspace, stream);
+  }
+
+  // Device status word of the plan (0 = ok); synchronises.
+  int device_status() {
+    int32_t code = 0;
+    if (plan_) xf_gemm_plan_device_status(plan_, &code);
+    return code;
+  }
+
+ private:
+  void release() {
+    if (plan_) xf_plan_destroy(plan_);
+    plan_ = nullptr;
+  }
+  // Harness buffers are managed memory (host-side verification reads them): bring the operands of
+  // the TMA copies to the GPU once, so the kernel's bulk copies never meet a non-resident page.
+  static void make_resident(xf_gemm_desc const& d, cudaStream_t stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return;
+    auto prefetch = [&](const void* p, size_t bytes) {
+      cudaPointerAttributes at;
+      if (cudaPointerGetAttributes(&at, p) == cudaSuccess && at.type == cudaMemoryTypeManaged)
+        cudaMemPrefetchAsync(p, bytes, dev, stream);
+      else
+        cudaGetLastError();
+    };
+    const size_t es = d.dtype_ab == XF_DT_S8 ? 1 : 2;
+    const size_t ds = d.dtype_d == XF_DT_BF16 ? 2 : 4;
+    const size_t la = d.batch_a ? d.L : 1, lb = d.batch_b ? d.L : 1;
+    prefetch(d.A, (la > 1 ? size_t(d.batch_a) * la : size_t(d.lda) * d.M) * es);
+    prefetch(d.B, (lb > 1 ? size_t(d.batch_b) * lb : size_t(d.ldb) * d.K) * es);
+    prefetch(d.D, (d.L > 1 ? size_t(d.batch_d) * d.L : size_t(d.ldd) * d.M) * ds);
+  }
+
+  xf_plan* plan_ = nullptr;
+  xefuse::Extensions ext_{};
+};
+
+}  // namespace cutlass::gemm::device
