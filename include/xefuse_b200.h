@@ -157,6 +157,10 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_FORCE_2CTA   4   /* always pair CTAs (cta_group::2) when the shape allows */
 #define XF_FLAG_FORCE_BN128  8   /* use the 128-column CTA tile */
 #define XF_FLAG_FORCE_BN256  16  /* use the 256-column CTA tile */
+#define XF_FLAG_FORCE_KS1    32  /* one 128-byte K slab per pipeline stage */
+#define XF_FLAG_FORCE_KS2    64  /* two 128-byte K slabs per pipeline stage */
+#define XF_FLAG_DIAG_NO_LOAD  256 /* timing diagnostics only: skip the TMA operand loads (D is garbage) */
+#define XF_FLAG_DIAG_NO_MMA   512 /* timing diagnostics only: skip the tensor-core MMAs (D is garbage) */
 
 typedef struct xf_plan xf_plan;
 

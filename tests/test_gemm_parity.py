@@ -73,23 +73,30 @@ def test_presets_ragged(preset, capi, oracle, cuda):
     check(capi, oracle, preset, 200, 336, 208, cuda)
 
 
-@pytest.mark.parametrize("flags_name", ["1cta_bn256", "2cta_bn256", "1cta_bn128", "2cta_bn128", "direct"])
+def _variant_flags(capi, name):
+    f = 0
+    f |= capi.FLAG_FORCE_1CTA if "1cta" in name else capi.FLAG_FORCE_2CTA if "2cta" in name else 0
+    f |= capi.FLAG_FORCE_BN256 if "bn256" in name else capi.FLAG_FORCE_BN128 if "bn128" in name else 0
+    f |= capi.FLAG_FORCE_KS1 if "ks1" in name else capi.FLAG_FORCE_KS2 if "ks2" in name else 0
+    f |= capi.FLAG_DIRECT_STORE if "direct" in name else 0
+    return f
+
+
+@pytest.mark.parametrize("flags_name", ["2cta_bn256_ks1", "2cta_bn256_ks2", "1cta_bn256_ks1", "2cta_bn128_ks1",
+                                        "2cta_bn128_ks2", "1cta_bn128_ks1", "1cta_bn128_ks2", "direct"])
 @pytest.mark.parametrize("preset", ["k2_compact", "k4v2_table", "k0a"])
 def test_every_kernel_variant(preset, flags_name, capi, oracle, cuda):
-    f = {"1cta_bn256": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN256,
-         "2cta_bn256": capi.FLAG_FORCE_2CTA | capi.FLAG_FORCE_BN256,
-         "1cta_bn128": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN128,
-         "2cta_bn128": capi.FLAG_FORCE_2CTA | capi.FLAG_FORCE_BN128,
-         "direct": capi.FLAG_DIRECT_STORE}[flags_name]
-    check(capi, oracle, preset, 512, 1024, 320, cuda, flags=f)
+    """Each compiled tile variant: 1 or 2 CTAs per tile, 128/256 columns, 1 or 2 K slabs per stage;
+    K = 320 is not a multiple of either stage depth."""
+    plan = check(capi, oracle, preset, 512, 1024, 320, cuda, flags=_variant_flags(capi, flags_name))
+    if flags_name != "direct":
+        assert ("cta2" in plan.kernel_name) == ("2cta" in flags_name)
 
 
-@pytest.mark.parametrize("flags_name", ["1cta_bn256", "2cta_bn256", "1cta_bn128"])
+@pytest.mark.parametrize("flags_name", ["2cta_bn256_ks1", "2cta_bn256_ks2", "1cta_bn256_ks1", "1cta_bn128_ks1",
+                                        "1cta_bn128_ks2"])
 def test_int8_variants(flags_name, capi, oracle, cuda):
-    f = {"1cta_bn256": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN256,
-         "2cta_bn256": capi.FLAG_FORCE_2CTA | capi.FLAG_FORCE_BN256,
-         "1cta_bn128": capi.FLAG_FORCE_1CTA | capi.FLAG_FORCE_BN128}[flags_name]
-    check(capi, oracle, "w8a8_dequant_biased", 512, 1024, 640, cuda, flags=f)
+    check(capi, oracle, "w8a8_dequant_biased", 512, 1024, 640, cuda, flags=_variant_flags(capi, flags_name))
 
 
 @pytest.mark.parametrize("shape", [(384, 768, 1024), (200, 336, 208), (128, 256, 128), (1, 16, 16)])

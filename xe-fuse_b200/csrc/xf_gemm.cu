@@ -72,23 +72,29 @@ static bool encode_3d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base,
 typedef void (*KernelFn)(const GemmParams);
 
 struct Variant {
-  int kind, bn, ctas, stages, smem;
+  int kind, bn, ctas, ks, stages, smem;
   KernelFn fn;
   const char* name;
 };
 
-#define XF_VARIANT(KIND, BN, CTAS, NAME)                                             \
-  {KIND, BN, CTAS, TileCfg<KIND, BN, CTAS>::STAGES, TileCfg<KIND, BN, CTAS>::SMEM_BYTES, \
-   gemm_evt_kernel<KIND, BN, CTAS>, NAME}
+#define XF_VARIANT(KIND, BN, CTAS, KS, NAME)                                                     \
+  {KIND, BN, CTAS, KS, TileCfg<KIND, BN, CTAS, KS>::STAGES, TileCfg<KIND, BN, CTAS, KS>::SMEM_BYTES, \
+   gemm_evt_kernel<KIND, BN, CTAS, KS>, NAME}
 
+// name = <dtype>_<cluster rows>x<columns>_cta<CTAs per tile>_k<K elements per stage>
 static const Variant g_variants[] = {
-    XF_VARIANT(0, 256, 2, "bf16_256x256_cta2"),
-    XF_VARIANT(0, 256, 1, "bf16_128x256_cta1"),
-    XF_VARIANT(0, 128, 2, "bf16_256x128_cta2"),
-    XF_VARIANT(0, 128, 1, "bf16_128x128_cta1"),
-    XF_VARIANT(1, 256, 2, "s8_256x256_cta2"),
-    XF_VARIANT(1, 256, 1, "s8_128x256_cta1"),
-    XF_VARIANT(1, 128, 1, "s8_128x128_cta1"),
+    XF_VARIANT(0, 256, 2, 1, "bf16_256x256_cta2_k64"),
+    XF_VARIANT(0, 256, 2, 2, "bf16_256x256_cta2_k128"),
+    XF_VARIANT(0, 256, 1, 1, "bf16_128x256_cta1_k64"),
+    XF_VARIANT(0, 128, 2, 1, "bf16_256x128_cta2_k64"),
+    XF_VARIANT(0, 128, 2, 2, "bf16_256x128_cta2_k128"),
+    XF_VARIANT(0, 128, 1, 1, "bf16_128x128_cta1_k64"),
+    XF_VARIANT(0, 128, 1, 2, "bf16_128x128_cta1_k128"),
+    XF_VARIANT(1, 256, 2, 1, "s8_256x256_cta2_k128"),
+    XF_VARIANT(1, 256, 2, 2, "s8_256x256_cta2_k256"),
+    XF_VARIANT(1, 256, 1, 1, "s8_128x256_cta1_k128"),
+    XF_VARIANT(1, 128, 1, 1, "s8_128x128_cta1_k128"),
+    XF_VARIANT(1, 128, 1, 2, "s8_128x128_cta1_k256"),
 };
 static const int g_num_variants = sizeof(g_variants) / sizeof(g_variants[0]);
 
@@ -270,11 +276,17 @@ static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
     if ((d->flags & XF_FLAG_FORCE_2CTA) && v.ctas != 2) continue;
     if ((d->flags & XF_FLAG_FORCE_BN128) && v.bn != 128) continue;
     if ((d->flags & XF_FLAG_FORCE_BN256) && v.bn != 256) continue;
+    if ((d->flags & XF_FLAG_FORCE_KS1) && v.ks != 1) continue;
+    if ((d->flags & XF_FLAG_FORCE_KS2) && v.ks != 2) continue;
     const int tiles = ceil_div(d->M, 128 * v.ctas) * ceil_div(d->N, v.bn) * d->L;
     const int units = sm_count / v.ctas;
     const int waves = ceil_div(tiles, units);
-    // relative time of one tile on its unit (lower is better per unit of work)
-    double eff = (v.bn == 256 ? 1.0 : 0.88) * (v.ctas == 2 ? 1.0 : 0.93);
+    // Measured throughput of each variant on a large bf16 problem (4096 x 28672 x 4096 on B200),
+    // relative to the paired 256x256 tile with 128-element K stages.  Narrow tiles and short
+    // stages pay the per-stage barrier hand-off more often and re-read operands from L2 more.
+    double eff;
+    if (v.bn == 256) eff = v.ctas == 2 ? (v.ks == 2 ? 1.00 : 0.91) : 0.84;
+    else eff = v.ctas == 2 ? (v.ks == 2 ? 0.67 : 0.48) : (v.ks == 2 ? 0.72 : 0.55);
     double tile_work = 128.0 * v.bn;  // per SM
     double cost = waves * tile_work / eff;
     if (!best || cost < best_cost * 0.999) {
@@ -309,7 +321,8 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   GemmParams& p = plan->params;
   memset(&p, 0, sizeof(p));
   const int es = elem_size(d->dtype_ab);
-  const int kblk = 128 / es;
+  const int kslab = 128 / es;            // K elements per 128-byte slab (A box width)
+  const int kblk = kslab * v->ks;        // K elements per pipeline stage (B box height)
   const int grp_cols = 128 / es;
   p.M = d->M; p.N = d->N; p.K = d->K; p.L = d->L;
   p.tiles_m = ceil_div(d->M, 128 * v->ctas);
@@ -339,13 +352,14 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   const bool tma_store_ok = d->dtype_d == XF_DT_BF16 && aligned16(d->D) && (d->ldd * 2) % 16 == 0 &&
                             (d->batch_d * 2) % 16 == 0 && !(d->flags & XF_FLAG_DIRECT_STORE);
   p.direct_store = tma_store_ok ? 0 : 1;
+  p.diag = ((d->flags & XF_FLAG_DIAG_NO_LOAD) ? 1 : 0) | ((d->flags & XF_FLAG_DIAG_NO_MMA) ? 2 : 0);
 
   const CUtensorMapDataType dt =
       d->dtype_ab == XF_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const uint64_t la = p.a_batched ? d->L : 1, lb = p.b_batched ? d->L : 1;
   const uint64_t sa2 = p.a_batched ? (uint64_t)d->batch_a * es : (uint64_t)d->lda * es * d->M;
   const uint64_t sb2 = p.b_batched ? (uint64_t)d->batch_b * es : (uint64_t)d->ldb * es * d->K;
-  if (!encode_3d(&p.tm_a, dt, d->A, d->K, d->M, la, (uint64_t)d->lda * es, sa2, kblk, 128,
+  if (!encode_3d(&p.tm_a, dt, d->A, d->K, d->M, la, (uint64_t)d->lda * es, sa2, kslab, 128,
                  CU_TENSOR_MAP_SWIZZLE_128B))
     return XF_ERR_INTERNAL;
   if (!encode_3d(&p.tm_b, dt, d->B, d->N, d->K, lb, (uint64_t)d->ldb * es, sb2, grp_cols, kblk,

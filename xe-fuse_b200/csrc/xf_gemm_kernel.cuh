@@ -27,19 +27,22 @@
 
 namespace xf {
 
-template <int KIND, int BN_, int CTAS_>
+template <int KIND, int BN_, int CTAS_, int KS_>
 struct TileCfg {
   static constexpr int BN = BN_;
   static constexpr int CTAS = CTAS_;
+  static constexpr int KS = KS_;                       // 128-byte K slabs per pipeline stage
   static constexpr int BM = 128;                       // rows per CTA
   static constexpr int ES = (KIND == 0) ? 2 : 1;       // bytes per A/B element
-  static constexpr int KBLK = 128 / ES;                // K elements per stage (128 B of K)
+  static constexpr int KSLAB = 128 / ES;               // K elements in one 128-byte slab
+  static constexpr int KBLK = KS * KSLAB;              // K elements per stage
   static constexpr int UK = 32 / ES;                   // K elements per tcgen05.mma
   static constexpr int BN_CTA = BN / CTAS;             // B columns one CTA loads
   static constexpr int GRP_COLS = 128 / ES;            // columns per 128-B group
   static constexpr int NGRP = BN_CTA / GRP_COLS;       // column groups per CTA
-  static constexpr int GRP_BYTES = KBLK * 128;
-  static constexpr int A_BYTES = BM * 128;
+  static constexpr int GRP_BYTES = KBLK * 128;         // one column group: KBLK rows of 128 B
+  static constexpr int A_SLAB_BYTES = BM * 128;        // 128 rows x 128 B of K
+  static constexpr int A_BYTES = KS * A_SLAB_BYTES;
   static constexpr int B_BYTES = NGRP * GRP_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BUF_BYTES = 2048;           // 32 rows x 64 B
@@ -262,10 +265,10 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
   }
 }
 
-template <int KIND, int BN, int CTAS>
+template <int KIND, int BN, int CTAS, int KS>
 __global__ void __launch_bounds__(256, 1)
 gemm_evt_kernel(const __grid_constant__ GemmParams p) {
-  using C = TileCfg<KIND, BN, CTAS>;
+  using C = TileCfg<KIND, BN, CTAS, KS>;
   constexpr int STAGES = C::STAGES;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -339,10 +342,18 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           }
           const uint32_t my_full = ptx::smem_u32(&full_bar[stage]);
           const uint32_t full_addr = (CTAS == 2) ? ptx::mapa(my_full, 0) : my_full;
+          if (p.diag & 1) {  // diagnostics: no operand traffic, the stage is "full" at once
+            if (cta_rank == 0) ptx::mbar_arrive(my_full);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           if (cta_rank == 0) ptx::mbar_arrive_expect_tx(my_full, C::STAGE_BYTES * CTAS);
           uint8_t* sa = stage_base + stage * C::STAGE_BYTES;
           uint8_t* sb = sa + C::A_BYTES;
-          ptx::tma_load_3d<CTAS>(ptx::smem_u32(sa), &p.tm_a, full_addr, kb * C::KBLK, row0, la);
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks)
+            ptx::tma_load_3d<CTAS>(ptx::smem_u32(sa + ks * C::A_SLAB_BYTES), &p.tm_a, full_addr,
+                                   kb * C::KBLK + ks * C::KSLAB, row0, la);
 #pragma unroll
           for (int g = 0; g < C::NGRP; ++g)
             ptx::tma_load_3d<CTAS>(ptx::smem_u32(sb + g * C::GRP_BYTES), &p.tm_b, full_addr,
@@ -378,10 +389,14 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t sb = sa + C::A_BYTES;
           const uint64_t adesc = ptx::make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t bdesc = ptx::make_smem_desc_sw128(sb, C::GRP_BYTES, 1024);
+          constexpr int MMAS_PER_SLAB = C::KSLAB / C::UK;  // 4
 #pragma unroll
-          for (int k = 0; k < C::KBLK / C::UK; ++k) {
-            // A: +32 B along K inside the 128-B swizzled row; B: +UK rows of 128 B
-            ptx::umma<KIND, CTAS>(d_tmem, adesc + static_cast<uint64_t>(k * (32 >> 4)),
+          for (int k = 0; k < KS * MMAS_PER_SLAB; ++k) {
+            if (p.diag & 2) break;  // diagnostics: barrier traffic only
+            // A: next slab every 4 MMAs, +32 B along K inside the 128-B swizzled row;
+            // B: +UK rows of 128 B per MMA
+            const int a_off = (k / MMAS_PER_SLAB) * C::A_SLAB_BYTES + (k % MMAS_PER_SLAB) * 32;
+            ptx::umma<KIND, CTAS>(d_tmem, adesc + static_cast<uint64_t>(a_off >> 4),
                                   bdesc + static_cast<uint64_t>(k * ((C::UK * 128) >> 4)), idesc,
                                   (kb | k) != 0 ? 1u : 0u);
           }

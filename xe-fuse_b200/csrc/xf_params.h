@@ -62,6 +62,7 @@ struct alignas(64) GemmParams {
   long long ldd, batch_d;
   int d_dtype;             // DT_BF16 / DT_F32 / DT_S32
   int direct_store;        // 1: plain global stores for D
+  int diag;                // diagnostics: bit0 skip the TMA loads, bit1 skip the MMAs (results are garbage)
   int* status;             // device status word (may be null)
   long long wait_budget;   // clock64 cycles a wait may take before giving up
   EpiParams epi;
