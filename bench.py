@@ -32,7 +32,8 @@ sys.path.insert(0, ROOT)
 
 METRIC = "fused GEMM+epilogue TFLOP/s"
 
-# name -> list of stages: (preset, M, N, K, dtype)
+# name -> list of stages: (preset, M, N, K, dtype[, "chain"]); a "chain" stage contracts over the
+# previous stage's output (all-gathered across ranks when the columns are sharded)
 WORKLOADS = {
     "k1": [("k1", 512, 4096, 4096, "bf16")],
     "k2": [("k2", 4096, 28672, 4096, "bf16")],
@@ -41,7 +42,7 @@ WORKLOADS = {
     "w8a8": [("w8a8", 8192, 8192, 28672, "s8")],
     # Llama-3-70B decoder-layer GEMM chain, M = 8192 tokens
     "pipeline": [("k4v2", 8192, 10240, 8192, "bf16"), ("k0a", 8192, 8192, 8192, "bf16"),
-                 ("k2", 8192, 57344, 8192, "bf16"), ("k0a", 8192, 8192, 28672, "bf16")],
+                 ("k2", 8192, 57344, 8192, "bf16"), ("k0a", 8192, 8192, 28672, "bf16", "chain")],
 }
 DESCR = {
     "k1": "k1 GEMM+RMSNorm row-scale M=512 N=4096 K=4096 bf16",
@@ -51,6 +52,14 @@ DESCR = {
     "w8a8": "w8a8_dequant_biased Llama-3-70B FFN down M=8192 K=28672 N=8192 int8 -> bf16, bf16 bias",
     "pipeline": "Llama-3-70B layer GEMM chain M=8192: QKV k4v2 (K=8192,N=10240), O k0a (8192,8192), "
                 "gate/up k2 (K=8192,N=57344), down k0a (K=28672,N=8192)",
+}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's kernel, from the
+# ncu captures summarised under profiles/ (full-size workloads, one GPU).
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    "k2": 506_583_296 + 107_739_392,       # profiles/gemm_evt_kernel_bf16_256x256_cta2_k128__k2_*.md
+    "w8a8": 1_990_824_000 + 129_954_816,   # profiles/gemm_evt_kernel_s8_256x256_cta2_k256__w8a8_*.md
 }
 
 
@@ -121,16 +130,20 @@ class ClockSampler:
 def gen_stage_host(stage, rank, world, seed):
     """Seeded host tensors of one stage for this rank's column shard (pinned where copied per step)."""
     import torch
-    preset, M, N, K, dt = stage
+    preset, M, N, K, dt = stage[:5]
+    chain = len(stage) > 5 and stage[5] == "chain"
     assert N % world == 0
     Ns = N // world
     g = torch.Generator().manual_seed(seed)
     gw = torch.Generator().manual_seed(seed * 7919 + 13 * rank + 1)   # per-shard weight stream
     h = {}
     if dt == "bf16":
-        X = torch.randn(M, K, generator=g, dtype=torch.float32)
-        h["R"] = torch.rsqrt((X * X).mean(dim=1) + 1e-6).contiguous()    # fp32 on the host
-        h["X"] = X.to(torch.bfloat16)
+        if chain:                      # activations come from the previous stage, on the device
+            h["X"], h["R"] = None, None
+        else:
+            X = torch.randn(M, K, generator=g, dtype=torch.float32)
+            h["R"] = torch.rsqrt((X * X).mean(dim=1) + 1e-6).contiguous()    # fp32 on the host
+            h["X"] = X.to(torch.bfloat16)
         W = torch.empty(K, Ns, dtype=torch.bfloat16)
         for k0 in range(0, K, 4096):                                      # bounded temporaries
             k1 = min(K, k0 + 4096)
@@ -165,20 +178,36 @@ def gen_stage_host(stage, rank, world, seed):
         cs[:, 0::2] = torch.cos(ang)
         cs[:, 1::2] = torch.sin(ang)
         h["cos_sin"] = cs.contiguous()
-    h["X"] = h["X"].contiguous().pin_memory() if torch.cuda.is_available() else h["X"].contiguous()
-    h["R"] = h["R"].pin_memory() if torch.cuda.is_available() else h["R"]
+    if h["X"] is not None:
+        h["X"] = h["X"].contiguous().pin_memory() if torch.cuda.is_available() else h["X"].contiguous()
+        h["R"] = h["R"].pin_memory() if torch.cuda.is_available() else h["R"]
     return h
 
 
-def build_stage_gpu(capi, stage, h, dev):
-    """Device buffers + the fused plan (and the unfused baseline's pieces) of one stage."""
+def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1):
+    """Device buffers + the fused plan of one stage.  With `share` (an earlier build of the same
+    stage) the static operands (weights, per-column vectors, tables) are reused and only the
+    per-step buffers (activations, row scales, output) are new: the second buffer set of the
+    pipelined end-to-end loop."""
     import torch
-    preset, M, N, K, dt = stage
+    preset, M, N, K, dt = stage[:5]
+    chain = len(stage) > 5 and stage[5] == "chain"
     Ns = h["W"].shape[1]
-    s = {"stage": stage, "Ns": Ns}
-    s["X"] = h["X"].to(dev, non_blocking=True)
-    s["R"] = h["R"].to(dev, non_blocking=True)
-    s["W"] = h["W"].to(dev)
+    s = {"stage": stage, "Ns": Ns, "chain": chain}
+    a_k_slabs = False
+    if chain:
+        # A = the previous stage's output: in place on one GPU, the all-gathered K slabs otherwise
+        if world == 1:
+            s["X"] = prev["D"]
+        else:
+            s["X"] = torch.empty((world,) + tuple(prev["D"].shape), dtype=torch.bfloat16, device=dev)
+            s["gather_from"] = prev["D"]
+            a_k_slabs = True
+        s["R"] = None
+    else:
+        s["X"] = h["X"].to(dev, non_blocking=True)
+        s["R"] = h["R"].to(dev, non_blocking=True)
+    s["W"] = share["W"] if share else h["W"].to(dev)
     kw = {}
     n_out = Ns
     if preset == "k1":
@@ -187,22 +216,23 @@ def build_stage_gpu(capi, stage, h, dev):
         kw = dict(row_scale=s["R"], pair="swiglu", compact=True)
         n_out = Ns // 2
     elif preset == "k4v2":
-        s["cos_sin"] = h["cos_sin"].to(dev)
+        s["cos_sin"] = share["cos_sin"] if share else h["cos_sin"].to(dev)
         kw = dict(row_scale=s["R"], pair="rope", cos_sin=s["cos_sin"], cos_sin_period=128)
     elif preset == "k0a":
-        s["residual"] = h["residual"].to(dev)
-        s["gamma"] = h["gamma"].to(dev)
+        s["residual"] = share["residual"] if share else h["residual"].to(dev)
+        s["gamma"] = share["gamma"] if share else h["gamma"].to(dev)
         kw = dict(residual=s["residual"], col_scale=s["gamma"])
     elif preset == "w8a8":
-        s["sc"] = h["sc"].to(dev)
-        s["bias"] = h["bias"].to(dev)
+        s["sc"] = share["sc"] if share else h["sc"].to(dev)
+        s["bias"] = share["bias"] if share else h["bias"].to(dev)
         kw = dict(row_scale=s["R"], col_scale=s["sc"], bias=s["bias"])
     s["D"] = torch.empty(M, n_out, dtype=torch.bfloat16, device=dev)
-    s["plan"] = capi.GemmPlan(s["X"], s["W"], s["D"], **kw)
+    s["plan"] = capi.GemmPlan(s["X"], s["W"], s["D"], a_k_slabs=a_k_slabs, **kw)
     s["flops"] = 2.0 * M * Ns * K
-    s["h2d_bytes"] = h["X"].numel() * h["X"].element_size() + h["R"].numel() * 4
+    s["h2d_bytes"] = 0 if chain else h["X"].numel() * h["X"].element_size() + h["R"].numel() * 4
     s["d2h_bytes"] = s["D"].numel() * 2
-    s["bytes_resident"] = (s["X"].numel() * s["X"].element_size() + s["W"].numel() * s["W"].element_size()
+    s["bytes_resident"] = ((0 if chain and world == 1 else s["X"].numel() * s["X"].element_size())
+                           + s["W"].numel() * s["W"].element_size()
                            + s["D"].numel() * 2)
     return s
 
@@ -211,7 +241,7 @@ def build_unfused(capi, s, dev):
     """Bare GEMM (identity epilogue) + the stand-alone kernel(s) the reference's unfused arm runs
     (autotune/pipeline_template.cpp.j2:771-797)."""
     import torch
-    preset, M, N, K, dt = s["stage"]
+    preset, M, N, K, dt = s["stage"][:5]
     Ns = s["Ns"]
     u = {}
     if dt == "s8":
@@ -224,7 +254,7 @@ def build_unfused(capi, s, dev):
         u["launches"] = 3
     else:
         u["out"] = torch.empty(M, Ns, dtype=torch.bfloat16, device=dev)
-        u["plan"] = capi.GemmPlan(s["X"], s["W"], u["out"])
+        u["plan"] = capi.GemmPlan(s["X"], s["W"], u["out"], a_k_slabs="gather_from" in s)
         if preset == "k1":
             u["post"] = lambda: capi.sa_scale_rows(u["out"], s["R"])
             u["launches"] = 2
@@ -277,7 +307,7 @@ def cpu_sample(stages, seconds_target, seed):
     cores = o.num_threads()
     # bound the sample by columns too so that the widened weight panel stays small
     plans = []
-    for (preset, M, N, K, dt) in stages:
+    for (preset, M, N, K, dt) in [st[:5] for st in stages]:
         Nc = min(N, 4096)
         plans.append((preset, M, Nc, K, dt))
     # calibrate on 16 rows
@@ -395,7 +425,9 @@ def main():
     l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
 
     host = [gen_stage_host(st, rank, world, seed=2024 + i) for i, st in enumerate(stages)]
-    gpu = [build_stage_gpu(capi, st, h, dev) for st, h in zip(stages, host)]
+    gpu = []
+    for st, h in zip(stages, host):
+        gpu.append(build_stage_gpu(capi, st, h, dev, prev=gpu[-1] if gpu else None, world=world))
     torch.cuda.synchronize()
     resident = sum(s["bytes_resident"] for s in gpu)
     flush = None
@@ -404,9 +436,14 @@ def main():
     flops_rank = sum(s["flops"] for s in gpu)
     flops_total = flops_rank * world
 
+    def run_stages(stage_list, stream=None):
+        for s in stage_list:
+            if "gather_from" in s:   # the one exchange of the path: output shards -> K slabs
+                xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
+            s["plan"].run(stream)
+
     def step():
-        for s in gpu:
-            s["plan"].run()
+        run_stages(gpu)
 
     def barrier():
         torch.cuda.synchronize()
@@ -439,20 +476,51 @@ def main():
     value = flops_total * args.steps / (ms * 1e-3) / 1e12
     ms_per_step = ms / args.steps
 
-    # ---- end to end through the C ABI with host buffers
-    outs = [torch.empty(s["D"].shape, dtype=torch.bfloat16).pin_memory() for s in gpu]
+    # ---- end to end through the C ABI with host buffers: every step copies its activations and
+    # row scales from pinned host memory and reads its whole output back.  Two device buffer sets
+    # and three streams (copy-in, compute, copy-out) let step i+1's upload and step i-1's read-back
+    # overlap step i's kernels, as a serving loop would; weights stay resident.
+    gpu2 = []
+    for st, h, s0 in zip(stages, host, gpu):
+        gpu2.append(build_stage_gpu(capi, st, h, dev, share=s0, prev=gpu2[-1] if gpu2 else None, world=world))
+    sets = [gpu, gpu2]
+    outs = [[torch.empty(s["D"].shape, dtype=torch.bfloat16).pin_memory() for s in gpu] for _ in range(2)]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_comp = torch.cuda.current_stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_k = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step():
-        for s, h, o in zip(gpu, host, outs):
-            s["X"].copy_(h["X"], non_blocking=True)
-            s["R"].copy_(h["R"], non_blocking=True)
-            s["plan"].run()
-            o.copy_(s["D"], non_blocking=True)
+    def e2e_loop(n):
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_k[b])            # the kernels that read this buffer set are done
+                for s, h in zip(sets[b], host):
+                    if not s["chain"]:
+                        s["X"].copy_(h["X"], non_blocking=True)
+                        s["R"].copy_(h["R"], non_blocking=True)
+                ev_in[b].record(s_in)
+            s_comp.wait_event(ev_in[b])
+            s_comp.wait_event(ev_out[b])            # the previous read-back of this output is done
+            run_stages(sets[b], s_comp.cuda_stream)
+            ev_k[b].record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k[b])
+                for s, o in zip(sets[b], outs[b]):
+                    o.copy_(s["D"], non_blocking=True)
+                ev_out[b].record(s_out)
+        s_comp.wait_stream(s_in)
+        s_comp.wait_stream(s_out)
 
-    for _ in range(3):
-        e2e_step()
+    e2e_loop(4)
     barrier()
-    ms_e2e = time_loop(torch, e2e_step, args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(s_comp)
+    e2e_loop(args.steps)
+    e1.record(s_comp)
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1)
     barrier()
     if dist is not None:
         t = torch.tensor([ms_e2e], device=dev)
@@ -461,7 +529,9 @@ def main():
     e2e = {"value": flops_total * args.steps / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
            "h2d_bytes_per_step": int(sum(s["h2d_bytes"] for s in gpu)),
            "d2h_bytes_per_step": int(sum(s["d2h_bytes"] for s in gpu)),
-           "ms_per_step": ms_e2e / args.steps}
+           "ms_per_step": ms_e2e / args.steps,
+           "how": "double-buffered: H2D of step i+1 and D2H of step i-1 overlap the kernels of step i"}
+    del gpu2, sets
 
     # ---- unfused baseline: bare GEMM + stand-alone kernel(s)
     unfused = None
@@ -504,12 +574,8 @@ def main():
                 if peaks.get("bf16_sustained") else None,
                 "frac_of_nominal": achieved / (4500.0 if is_s8 else 2250.0),
                 "kernel": ",".join(sorted({s["plan"].kernel_name for s in gpu}))}
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
-        try:
-            roofline["traffic"] = json.load(open(traffic_file)).get(args.workload)
-        except Exception:
-            pass
+    if world == 1:
+        roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
@@ -522,7 +588,9 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "s8" if is_s8 else "bf16", "data": "synthetic",
         "config": {"workload": DESCR[args.workload],
-                   "sharding": f"weight columns N split {world}-way, activations and row scales replicated, no collective inside a stage",
+                   "sharding": (f"weight columns N split {world}-way, activations and row scales replicated, no collective inside a stage"
+                                + ("; gate/up output shards all-gathered (NCCL) into K slabs for the down projection"
+                                   if world > 1 and any(s["chain"] for s in gpu) else "")),
                    "l2": ("L2 flushed before every timed step" if flush is not None else
                           f"resident inputs+outputs {resident >> 20} MiB > L2 {l2_bytes >> 20} MiB, no flush"),
                    "kernels": [s["plan"].kernel_name for s in gpu]},

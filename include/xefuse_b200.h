@@ -149,6 +149,12 @@ typedef struct xf_gemm_desc {
   int32_t tile_m, tile_n, tile_k; /* the caller's TileShape: a hint, mapped to a native CTA tile */
   int32_t flags;          /* XF_FLAG_* */
   xf_epilogue_desc epi;
+  /* A stored as K slabs (the all-gathered output of a column-sharded producer stage): element
+   * A[m,k] lives at A + (k / a_k_slab) * a_k_slab_stride + m * lda + (k % a_k_slab).  0 = A is one
+   * [M,K] matrix.  a_k_slab must be a multiple of 256 elements and divide K; needs L == 1. */
+  int32_t a_k_slab;
+  int32_t pad_;
+  int64_t a_k_slab_stride;
 } xf_gemm_desc;
 
 /* flags */

@@ -55,7 +55,8 @@ class XfGemmDesc(C.Structure):
                 ("B", C.c_void_p), ("ldb", C.c_int64), ("batch_b", C.c_int64),
                 ("D", C.c_void_p), ("ldd", C.c_int64), ("batch_d", C.c_int64),
                 ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
-                ("flags", C.c_int32), ("epi", XfEpilogueDesc)]
+                ("flags", C.c_int32), ("epi", XfEpilogueDesc),
+                ("a_k_slab", C.c_int32), ("pad_", C.c_int32), ("a_k_slab_stride", C.c_int64)]
 
 
 # Every symbol include/xefuse_b200.h declares (checked by the CPU test-suite).
@@ -153,13 +154,15 @@ class GemmPlan:
 
     def __init__(self, A, B, D, *, residual=None, aux_store=None, row_scale=None, col_scale=None,
                  bias=None, unary="none", pair="none", cos_sin=None, cos_sin_period=0,
-                 compact=False, flags=0, tile=(256, 256, 32)):
+                 compact=False, flags=0, tile=(256, 256, 32), a_k_slabs=False):
         import torch
         L_ = lib()
         self._keep = [A, B, D, residual, aux_store, row_scale, col_scale, bias, cos_sin]
-        batched = A.dim() == 3
+        batched = A.dim() == 3 and not a_k_slabs
         Lb = A.shape[0] if batched else 1
         M, K = A.shape[-2], A.shape[-1]
+        if a_k_slabs:          # A is [G][M, K/G]: the gathered output of G column shards
+            K = A.shape[0] * A.shape[2]
         N = B.shape[-1]
         d = XfGemmDesc()
         d.dtype_ab = _torch_dtype_code(A)
@@ -171,6 +174,8 @@ class GemmPlan:
         d.D, d.ldd, d.batch_d = D.data_ptr(), D.stride(-2), (D.stride(0) if D.dim() == 3 else 0)
         d.tile_m, d.tile_n, d.tile_k = tile
         d.flags = flags
+        if a_k_slabs:
+            d.a_k_slab, d.a_k_slab_stride = A.shape[2], A.stride(0)
         e = d.epi
         e.residual = mat(residual)
         e.aux_store = mat(aux_store)

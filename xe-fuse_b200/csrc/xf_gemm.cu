@@ -164,7 +164,7 @@ static xf_status validate(const xf_gemm_desc* d) {
     return XF_ERR_INVALID_PROBLEM;
   }
   const int es = elem_size(d->dtype_ab);
-  if (d->lda < d->K || d->ldb < d->N) {
+  if ((d->a_k_slab == 0 && d->lda < d->K) || d->ldb < d->N) {
     set_error("leading dimensions too small (lda=%lld K=%d, ldb=%lld N=%d)", (long long)d->lda, d->K,
               (long long)d->ldb, d->N);
     return XF_ERR_INVALID_LAYOUT;
@@ -174,6 +174,15 @@ static xf_status validate(const xf_gemm_desc* d) {
     set_error("A/B base pointers, row pitches and batch strides must be multiples of 16 bytes "
               "(lda=%lld ldb=%lld, %d-byte elements)", (long long)d->lda, (long long)d->ldb, es);
     return XF_ERR_MISALIGNED_OPERAND;
+  }
+  if (d->a_k_slab != 0) {
+    if (d->a_k_slab < 0 || d->a_k_slab % 256 != 0 || d->K % d->a_k_slab != 0 || d->L != 1 ||
+        d->lda < d->a_k_slab || (d->a_k_slab_stride * es) % 16 != 0) {
+      set_error("A in K slabs needs L == 1, a slab width that is a multiple of 256 and divides K, "
+                "lda >= slab width and a 16-byte aligned slab stride (slab=%d K=%d L=%d)",
+                d->a_k_slab, d->K, d->L);
+      return XF_ERR_INVALID_LAYOUT;
+    }
   }
   const xf_epilogue_desc& e = d->epi;
   const bool any_epi = e.residual.enabled || e.aux_store.enabled || e.row_scale.enabled ||
@@ -359,8 +368,13 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   const uint64_t la = p.a_batched ? d->L : 1, lb = p.b_batched ? d->L : 1;
   const uint64_t sa2 = p.a_batched ? (uint64_t)d->batch_a * es : (uint64_t)d->lda * es * d->M;
   const uint64_t sb2 = p.b_batched ? (uint64_t)d->batch_b * es : (uint64_t)d->ldb * es * d->K;
-  if (!encode_3d(&p.tm_a, dt, d->A, d->K, d->M, la, (uint64_t)d->lda * es, sa2, kslab, 128,
-                 CU_TENSOR_MAP_SWIZZLE_128B))
+  p.a_k_slab = d->a_k_slab;
+  if (d->a_k_slab > 0) {
+    if (!encode_3d(&p.tm_a, dt, d->A, d->a_k_slab, d->M, d->K / d->a_k_slab, (uint64_t)d->lda * es,
+                   (uint64_t)d->a_k_slab_stride * es, kslab, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+      return XF_ERR_INTERNAL;
+  } else if (!encode_3d(&p.tm_a, dt, d->A, d->K, d->M, la, (uint64_t)d->lda * es, sa2, kslab, 128,
+                        CU_TENSOR_MAP_SWIZZLE_128B))
     return XF_ERR_INTERNAL;
   if (!encode_3d(&p.tm_b, dt, d->B, d->N, d->K, lb, (uint64_t)d->ldb * es, sb2, grp_cols, kblk,
                  CU_TENSOR_MAP_SWIZZLE_128B))

@@ -351,9 +351,15 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           uint8_t* sa = stage_base + stage * C::STAGE_BYTES;
           uint8_t* sb = sa + C::A_BYTES;
 #pragma unroll
-          for (int ks = 0; ks < KS; ++ks)
-            ptx::tma_load_3d<CTAS>(ptx::smem_u32(sa + ks * C::A_SLAB_BYTES), &p.tm_a, full_addr,
-                                   kb * C::KBLK + ks * C::KSLAB, row0, la);
+          for (int ks = 0; ks < KS; ++ks) {
+            int ka = kb * C::KBLK + ks * C::KSLAB, a2 = la;
+            if (p.a_k_slab > 0) {  // A gathered from column shards: slab index is the third mode
+              a2 = ka / p.a_k_slab;
+              ka -= a2 * p.a_k_slab;
+            }
+            ptx::tma_load_3d<CTAS>(ptx::smem_u32(sa + ks * C::A_SLAB_BYTES), &p.tm_a, full_addr, ka,
+                                   row0, a2);
+          }
 #pragma unroll
           for (int g = 0; g < C::NGRP; ++g)
             ptx::tma_load_3d<CTAS>(ptx::smem_u32(sb + g * C::GRP_BYTES), &p.tm_b, full_addr,

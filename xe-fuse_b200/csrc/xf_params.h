@@ -58,6 +58,7 @@ struct alignas(64) GemmParams {
   int num_kb;              // ceil(K / KBLK)
   int group_m;             // rasterisation group height in cluster tiles
   int a_batched, b_batched;  // 0: batch stride 0, always use batch coordinate 0
+  int a_k_slab;            // >0: A is stored as K slabs of this many elements (third tensor-map mode)
   void* D;
   long long ldd, batch_d;
   int d_dtype;             // DT_BF16 / DT_F32 / DT_S32
