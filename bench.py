@@ -539,7 +539,9 @@ def main():
         us = [build_unfused(capi, s, dev) for s in gpu]
 
         def unfused_step():
-            for u in us:
+            for u, s in zip(us, gpu):
+                if "gather_from" in s:   # same exchange as the fused arm
+                    xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
                 u["plan"].run()
                 u["post"]()
 
