@@ -184,7 +184,7 @@ def gen_stage_host(stage, rank, world, seed):
     return h
 
 
-def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1):
+def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=None, consume=None):
     """Device buffers + the fused plan of one stage.  With `share` (an earlier build of the same
     stage) the static operands (weights, per-column vectors, tables) are reused and only the
     per-step buffers (activations, row scales, output) are new: the second buffer set of the
@@ -199,6 +199,10 @@ def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1):
         # A = the previous stage's output: in place on one GPU, the all-gathered K slabs otherwise
         if world == 1:
             s["X"] = prev["D"]
+        elif consume is not None:      # slabs already filled by the producer's epilogue (peer stores)
+            s["X"] = consume.tensor
+            s["barrier"] = consume
+            a_k_slabs = True
         else:
             s["X"] = torch.empty((world,) + tuple(prev["D"].shape), dtype=torch.bfloat16, device=dev)
             s["gather_from"] = prev["D"]
@@ -226,7 +230,11 @@ def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1):
         s["sc"] = share["sc"] if share else h["sc"].to(dev)
         s["bias"] = share["bias"] if share else h["bias"].to(dev)
         kw = dict(row_scale=s["R"], col_scale=s["sc"], bias=s["bias"])
-    s["D"] = torch.empty(M, n_out, dtype=torch.bfloat16, device=dev)
+    if gather is not None:             # D is this rank's slab of the symmetric gathered buffer
+        s["D"] = gather.local_shard
+        kw["d_peer_ptrs"] = gather.peer_slab_ptrs()
+    else:
+        s["D"] = torch.empty(M, n_out, dtype=torch.bfloat16, device=dev)
     s["plan"] = capi.GemmPlan(s["X"], s["W"], s["D"], a_k_slabs=a_k_slabs, **kw)
     s["flops"] = 2.0 * M * Ns * K
     s["h2d_bytes"] = 0 if chain else h["X"].numel() * h["X"].element_size() + h["R"].numel() * 4
@@ -388,6 +396,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="k2", choices=sorted(WORKLOADS))
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N>1, chained stages: all-gather fused into the producer's epilogue "
+                         "(peer stores) or a separate ncclAllGather")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-unfused", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -425,9 +436,24 @@ def main():
     l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
 
     host = [gen_stage_host(st, rank, world, seed=2024 + i) for i, st in enumerate(stages)]
-    gpu = []
-    for st, h in zip(stages, host):
-        gpu.append(build_stage_gpu(capi, st, h, dev, prev=gpu[-1] if gpu else None, world=world))
+
+    def build_set(share_from=None):
+        """One set of per-step buffers + plans for all stages.  When a stage feeds a chained
+        consumer on several GPUs, its output goes to a symmetric gathered buffer: fused into the
+        producer's epilogue (--gather fused) or by ncclAllGather afterwards (--gather nccl)."""
+        out, pending = [], None
+        for i, (st, h) in enumerate(zip(stages, host)):
+            nxt_chain = i + 1 < len(stages) and len(stages[i + 1]) > 5
+            gather = None
+            if nxt_chain and world > 1 and args.gather == "fused":
+                n_out = (st[2] // world) // (2 if st[0] == "k2" else 1)
+                gather = xf.sharding.GatherBuffer(dist, st[1], n_out, torch.bfloat16, dev)
+            out.append(build_stage_gpu(capi, st, h, dev, share=share_from[i] if share_from else None,
+                                       prev=out[-1] if out else None, world=world, gather=gather, consume=pending))
+            pending = gather
+        return out
+
+    gpu = build_set()
     torch.cuda.synchronize()
     resident = sum(s["bytes_resident"] for s in gpu)
     flush = None
@@ -440,6 +466,8 @@ def main():
         for s in stage_list:
             if "gather_from" in s:   # the one exchange of the path: output shards -> K slabs
                 xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
+            if "barrier" in s:       # slabs were written by the producers' epilogues: wait for all
+                s["barrier"].barrier()
             s["plan"].run(stream)
 
     def step():
@@ -480,9 +508,7 @@ def main():
     # row scales from pinned host memory and reads its whole output back.  Two device buffer sets
     # and three streams (copy-in, compute, copy-out) let step i+1's upload and step i-1's read-back
     # overlap step i's kernels, as a serving loop would; weights stay resident.
-    gpu2 = []
-    for st, h, s0 in zip(stages, host, gpu):
-        gpu2.append(build_stage_gpu(capi, st, h, dev, share=s0, prev=gpu2[-1] if gpu2 else None, world=world))
+    gpu2 = build_set(share_from=gpu)
     sets = [gpu, gpu2]
     outs = [[torch.empty(s["D"].shape, dtype=torch.bfloat16).pin_memory() for s in gpu] for _ in range(2)]
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
@@ -542,6 +568,8 @@ def main():
             for u, s in zip(us, gpu):
                 if "gather_from" in s:   # same exchange as the fused arm
                     xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
+                if "barrier" in s:       # unfused arm: gather the fused producer's slab with NCCL
+                    xf.sharding.all_gather_shards(dist, s["barrier"].local_shard, s["X"])
                 u["plan"].run()
                 u["post"]()
 
@@ -591,7 +619,8 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "s8" if is_s8 else "bf16", "data": "synthetic",
         "config": {"workload": DESCR[args.workload],
                    "sharding": (f"weight columns N split {world}-way, activations and row scales replicated, no collective inside a stage"
-                                + ("; gate/up output shards all-gathered (NCCL) into K slabs for the down projection"
+                                + ((f"; gate/up output shards all-gathered into K slabs for the down projection "
+                                    f"({'peer stores from the epilogue' if args.gather == 'fused' else 'ncclAllGather'})")
                                    if world > 1 and any(s["chain"] for s in gpu) else "")),
                    "l2": ("L2 flushed before every timed step" if flush is not None else
                           f"resident inputs+outputs {resident >> 20} MiB > L2 {l2_bytes >> 20} MiB, no flush"),

@@ -153,8 +153,12 @@ typedef struct xf_gemm_desc {
    * A[m,k] lives at A + (k / a_k_slab) * a_k_slab_stride + m * lda + (k % a_k_slab).  0 = A is one
    * [M,K] matrix.  a_k_slab must be a multiple of 256 elements and divide K; needs L == 1. */
   int32_t a_k_slab;
-  int32_t pad_;
+  int32_t num_d_peer;     /* 0..7 further destinations of the output */
   int64_t a_k_slab_stride;
+  /* Further copies of D, with D's ldd/batch_d: every output tile is also stored to each of them
+   * from the epilogue.  With pointers into the other GPUs' gathered buffers (peer-mapped memory)
+   * this is the all-gather of column shards, overlapped with the GEMM instead of following it. */
+  void* D_peer[7];
 } xf_gemm_desc;
 
 /* flags */

@@ -110,3 +110,43 @@ def test_consumer_reads_gathered_k_slabs_on_gpu(capi, oracle, cuda):
         assert plan.device_status() == 0
         want = oracle.epilogue(oracle.gemm_bf16(A, B), residual=res, col=gamma)
         assert pc.compare_bf16(oracle, bf16_bits(D), want)[0] == 0, plan.kernel_name
+
+
+@pytest.mark.gpu
+def test_output_copies_from_the_epilogue_on_gpu(capi, oracle, cuda):
+    """xf_gemm_desc.D_peer: every output tile is also stored to the extra destinations (here local
+    buffers standing in for the peers' gathered slabs), for TMA and for plain stores."""
+    import torch
+    import parity_cases as pc
+    from conftest import bf16_bits
+    d = pc.make_inputs(oracle, "k2_compact", 392, 640, 200, 13)
+    _, want = pc.expected(oracle, "k2_compact", d)
+    t = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(cuda)
+    A, B, R = t(d["A"]), t(d["B"]), torch.from_numpy(d["scale"]).to(cuda)
+    for flags in (0, capi.FLAG_DIRECT_STORE):
+        D = torch.zeros((392, 320), dtype=torch.bfloat16, device=cuda)
+        copies = [torch.zeros_like(D) for _ in range(3)]
+        plan = capi.GemmPlan(A, B, D, row_scale=R, pair="swiglu", compact=True, flags=flags,
+                             d_peer_ptrs=[c.data_ptr() for c in copies])
+        plan.run()
+        torch.cuda.synchronize()
+        assert plan.device_status() == 0
+        assert pc.compare_bf16(oracle, bf16_bits(D), want)[0] == 0
+        for c in copies:
+            assert torch.equal(c.view(torch.int16), D.view(torch.int16))
+
+
+@pytest.mark.gpu
+def test_sharded_stages_with_fused_and_nccl_gather_on_2_gpus(capi, oracle, cuda):
+    """Needs two GPUs on the box: producer shards -> gathered K slabs (peer stores from the
+    epilogue, and ncclAllGather) -> consumer, every rank checked against the oracle."""
+    import subprocess
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU visible: the 2-rank check needs two")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300),
+                        os.path.join(ROOT, "tests", "multi_gpu_check.py")],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "MULTI_GPU_CHECK PASSED" in r.stdout, r.stdout[-3000:]

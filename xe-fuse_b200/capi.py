@@ -56,7 +56,8 @@ class XfGemmDesc(C.Structure):
                 ("D", C.c_void_p), ("ldd", C.c_int64), ("batch_d", C.c_int64),
                 ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
                 ("flags", C.c_int32), ("epi", XfEpilogueDesc),
-                ("a_k_slab", C.c_int32), ("pad_", C.c_int32), ("a_k_slab_stride", C.c_int64)]
+                ("a_k_slab", C.c_int32), ("num_d_peer", C.c_int32), ("a_k_slab_stride", C.c_int64),
+                ("D_peer", C.c_void_p * 7)]
 
 
 # Every symbol include/xefuse_b200.h declares (checked by the CPU test-suite).
@@ -154,7 +155,7 @@ class GemmPlan:
 
     def __init__(self, A, B, D, *, residual=None, aux_store=None, row_scale=None, col_scale=None,
                  bias=None, unary="none", pair="none", cos_sin=None, cos_sin_period=0,
-                 compact=False, flags=0, tile=(256, 256, 32), a_k_slabs=False):
+                 compact=False, flags=0, tile=(256, 256, 32), a_k_slabs=False, d_peer_ptrs=()):
         import torch
         L_ = lib()
         self._keep = [A, B, D, residual, aux_store, row_scale, col_scale, bias, cos_sin]
@@ -176,6 +177,9 @@ class GemmPlan:
         d.flags = flags
         if a_k_slabs:
             d.a_k_slab, d.a_k_slab_stride = A.shape[2], A.stride(0)
+        d.num_d_peer = len(d_peer_ptrs)        # raw device pointers of further copies of D
+        for i, ptr in enumerate(d_peer_ptrs):
+            d.D_peer[i] = ptr
         e = d.epi
         e.residual = mat(residual)
         e.aux_store = mat(aux_store)

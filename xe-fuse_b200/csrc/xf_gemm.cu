@@ -184,6 +184,20 @@ static xf_status validate(const xf_gemm_desc* d) {
       return XF_ERR_INVALID_LAYOUT;
     }
   }
+  if (d->num_d_peer < 0 || d->num_d_peer > 7) {
+    set_error("num_d_peer must be 0..7 (got %d)", d->num_d_peer);
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  for (int c = 0; c < d->num_d_peer; ++c) {
+    if (!d->D_peer[c] || d->dtype_d != XF_DT_BF16) {
+      set_error("peer outputs must be non-null and bf16");
+      return XF_ERR_INVALID_PROBLEM;
+    }
+    if (!aligned16(d->D_peer[c]) != !aligned16(d->D)) {
+      set_error("peer outputs must have the alignment of D");
+      return XF_ERR_MISALIGNED_OPERAND;
+    }
+  }
   const xf_epilogue_desc& e = d->epi;
   const bool any_epi = e.residual.enabled || e.aux_store.enabled || e.row_scale.enabled ||
                        e.col_scale.enabled || e.bias.enabled || e.unary != XF_UNARY_NONE ||
@@ -384,6 +398,16 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
     if (!encode_3d(&p.tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d->D, n_out, d->M, d->L,
                    (uint64_t)d->ldd * 2, sd2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
       return XF_ERR_INTERNAL;
+  }
+  p.num_d_peer = d->num_d_peer;
+  for (int c = 0; c < d->num_d_peer; ++c) {
+    p.D_peer[c] = d->D_peer[c];
+    if (!p.direct_store) {
+      const uint64_t sd2 = d->L > 1 ? (uint64_t)d->batch_d * 2 : (uint64_t)d->ldd * 2 * d->M;
+      if (!encode_3d(&p.tm_d_peer[c], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d->D_peer[c], n_out, d->M, d->L,
+                     (uint64_t)d->ldd * 2, sd2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+        return XF_ERR_INTERNAL;
+    }
   }
 
   cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(v->fn),

@@ -553,6 +553,12 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
                                 static_cast<long long>(l) * p.batch_d +
                                 static_cast<long long>(row) * p.ldd + out_col0;
             store_bf16_row(dp, pk, n_out - out_col0, 32);
+            for (int c = 0; c < p.num_d_peer; ++c) {
+              __nv_bfloat16* pp = reinterpret_cast<__nv_bfloat16*>(p.D_peer[c]) +
+                                  static_cast<long long>(l) * p.batch_d +
+                                  static_cast<long long>(row) * p.ldd + out_col0;
+              store_bf16_row(pp, pk, n_out - out_col0, 32);
+            }
           }
         } else if (warp_rows_ok) {
           if (lane == 0) ptx::tma_store_wait_read<1>();  // the buffer used two stores ago is free
@@ -567,6 +573,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           __syncwarp();
           if (lane == 0) {
             ptx::tma_store_3d(&p.tm_d, ptx::smem_u32(sbuf), out_col0, m0 + q * 32, l);
+            // the same tile into every peer's gathered buffer: the all-gather rides on the epilogue
+            for (int c = 0; c < p.num_d_peer; ++c)
+              ptx::tma_store_3d(&p.tm_d_peer[c], ptx::smem_u32(sbuf), out_col0, m0 + q * 32, l);
             ptx::tma_store_commit();
           }
           sidx ^= 1;

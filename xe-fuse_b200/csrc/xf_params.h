@@ -53,6 +53,7 @@ struct alignas(64) GemmParams {
   CUtensorMap tm_a;   // [L][M][K], box {128 B of K, 128 rows}, 128-B swizzle
   CUtensorMap tm_b;   // [L][K][N], box {128 B of N, KBLK rows}, 128-B swizzle
   CUtensorMap tm_d;   // [L][M][Nout] bf16, box {32 cols, 32 rows}, 64-B swizzle
+  CUtensorMap tm_d_peer[7];  // further copies of D (other GPUs' gathered buffers), same geometry
   int M, N, K, L;
   int tiles_m, tiles_n;    // in units of the cluster tile (128*CTAS rows x BN columns)
   int num_kb;              // ceil(K / KBLK)
@@ -60,6 +61,8 @@ struct alignas(64) GemmParams {
   int a_batched, b_batched;  // 0: batch stride 0, always use batch coordinate 0
   int a_k_slab;            // >0: A is stored as K slabs of this many elements (third tensor-map mode)
   void* D;
+  void* D_peer[7];         // further destinations of the same output (peer-mapped memory)
+  int num_d_peer;          // 0..7
   long long ldd, batch_d;
   int d_dtype;             // DT_BF16 / DT_F32 / DT_S32
   int direct_store;        // 1: plain global stores for D

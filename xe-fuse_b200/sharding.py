@@ -55,3 +55,43 @@ def slabs_to_matrix(gathered):
     """[G][M, Ns] -> the logical [M, G*Ns] matrix (host-side check helper; copies)."""
     g, m, ns = gathered.shape
     return gathered.permute(1, 0, 2).reshape(m, g * ns)
+
+
+class GatherBuffer:
+    """The [G][M, Ns] gathered buffer of a column-sharded stage in symmetric (peer-mapped) memory.
+
+    Every rank allocates the same buffer and exchanges handles once; afterwards rank r's producer
+    GEMM stores each output tile into slab r of EVERY rank's buffer straight from its epilogue
+    (xf_gemm_desc.D_peer), so the all-gather overlaps the GEMM instead of following it.  A
+    stream-ordered barrier across the ranks then releases the consumer stage, which reads only its
+    own (local) copy.  Collective: all ranks construct it, and call barrier(), in the same order.
+    """
+
+    def __init__(self, dist, m_rows, shard_cols, dtype, device, group=None):
+        import torch
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.tensor = symm.empty((self.world, m_rows, shard_cols), dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.tensor, group=self.group)
+        self.slab_bytes = m_rows * shard_cols * self.tensor.element_size()
+        self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.base_ptrs) != self.world:
+            raise RuntimeError("symmetric memory rendezvous returned %d pointers for %d ranks"
+                               % (len(self.base_ptrs), self.world))
+
+    @property
+    def local_shard(self):
+        """This rank's slab of its own buffer: the producer stage's D."""
+        return self.tensor[self.rank]
+
+    def peer_slab_ptrs(self):
+        """Device pointers of slab `rank` in every OTHER rank's buffer (mapped into this process)."""
+        off = self.rank * self.slab_bytes
+        return [p + off for g, p in enumerate(self.base_ptrs) if g != self.rank]
+
+    def barrier(self):
+        """Stream-ordered barrier: returns (on the current stream) once every rank's work enqueued
+        before its own barrier() has finished, i.e. once all slabs of the local buffer are complete."""
+        self.handle.barrier(channel=0)
