@@ -1,0 +1,50 @@
+"""B200 tile selection, behind the reference selector's interface.
+
+`select_tile(M, N, K, kernel="bare", groups=1) -> str` keeps the signature and the return format
+(a `cute::Shape<>` argument string such as "_256, _256, _32") of the reference's
+autotune/tile_selector.py:48, so generate_kernel.py / generate_pipeline.py can import this module
+in its place.  On B200 the TileShape of a kernel is only a hint: the library maps it to a native
+CTA tile.  `native_tile()` mirrors that choice (select_variant in csrc/xf_gemm.cu): the cost of a
+variant is waves x tile area / measured efficiency, over the compiled variants
+
+    (columns, CTAs per tile, 128-byte K slabs per stage): rows = 128 x CTAs
+
+The efficiencies were measured on a 4096 x 28672 x 4096 bf16 GEMM on B200.
+"""
+from math import ceil
+
+SM_COUNT = 148
+
+# (bn, ctas, ks) -> relative throughput; order = the library's variant table
+BF16_VARIANTS = [((256, 2, 1), 0.91), ((256, 2, 2), 1.00), ((256, 1, 1), 0.84), ((128, 2, 1), 0.48),
+                 ((128, 2, 2), 0.67), ((128, 1, 1), 0.55), ((128, 1, 2), 0.72)]
+S8_VARIANTS = [((256, 2, 1), 0.91), ((256, 2, 2), 1.00), ((256, 1, 1), 0.84), ((128, 1, 1), 0.55),
+               ((128, 1, 2), 0.72)]
+
+
+def native_tile(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT):
+    """(rows, columns, ctas, k_elements_per_stage) of the kernel variant the library picks."""
+    best, best_cost = None, None
+    for (bn, ctas, ks), eff in (S8_VARIANTS if dtype in ("s8", "int8") else BF16_VARIANTS):
+        tiles = ceil(M / (128 * ctas)) * ceil(N / bn) * L
+        waves = ceil(tiles / (sm_count // ctas))
+        cost = waves * 128.0 * bn / eff
+        if best is None or cost < best_cost * 0.999:
+            best, best_cost = (bn, ctas, ks), cost
+    bn, ctas, ks = best
+    kslab = 128 if dtype in ("s8", "int8") else 64
+    return 128 * ctas, bn, ctas, ks * kslab
+
+
+def kernel_name(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT):
+    """Name the library reports for that variant (xf_gemm_plan_kernel_name without the stage count)."""
+    rows, bn, ctas, kstage = native_tile(M, N, K, dtype, L, sm_count)
+    return f"{'s8' if dtype in ('s8', 'int8') else 'bf16'}_{rows}x{bn}_cta{ctas}_k{kstage}"
+
+
+def select_tile(M: int, N: int, K: int, kernel: str = "bare", groups: int = 1) -> str:
+    """TileShape string for the kernel generators: the native (rows, columns) with the reference's
+    K extent of 32 -- every value is one of the extents the reference's tile list uses."""
+    dtype = "s8" if "w8a8" in kernel else "bf16"
+    rows, bn, _, _ = native_tile(M, N, K, dtype)
+    return f"_{rows}, _{bn}, _32"
