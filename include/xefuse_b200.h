@@ -171,6 +171,7 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_FORCE_KS2    64  /* two 128-byte K slabs per pipeline stage */
 #define XF_FLAG_DIAG_NO_LOAD  256 /* timing diagnostics only: skip the TMA operand loads (D is garbage) */
 #define XF_FLAG_DIAG_NO_MMA   512 /* timing diagnostics only: skip the tensor-core MMAs (D is garbage) */
+#define XF_FLAG_DIAG_NO_EPILOGUE 1024 /* timing diagnostics only: drain TMEM, compute and store nothing */
 
 typedef struct xf_plan xf_plan;
 

@@ -375,7 +375,8 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   const bool tma_store_ok = d->dtype_d == XF_DT_BF16 && aligned16(d->D) && (d->ldd * 2) % 16 == 0 &&
                             (d->batch_d * 2) % 16 == 0 && !(d->flags & XF_FLAG_DIRECT_STORE);
   p.direct_store = tma_store_ok ? 0 : 1;
-  p.diag = ((d->flags & XF_FLAG_DIAG_NO_LOAD) ? 1 : 0) | ((d->flags & XF_FLAG_DIAG_NO_MMA) ? 2 : 0);
+  p.diag = ((d->flags & XF_FLAG_DIAG_NO_LOAD) ? 1 : 0) | ((d->flags & XF_FLAG_DIAG_NO_MMA) ? 2 : 0) |
+           ((d->flags & XF_FLAG_DIAG_NO_EPILOGUE) ? 4 : 0) | ((d->flags & 2048) ? 8 : 0);
 
   const CUtensorMapDataType dt =
       d->dtype_ab == XF_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
@@ -422,7 +423,7 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
     // number of CTA pairs that can be co-resident (GPC boundaries may leave an SM unpaired)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count - (sm_count & 1), 1, 1);
-    cfg.blockDim = dim3(256, 1, 1);
+    cfg.blockDim = dim3(384, 1, 1);
     cfg.dynamicSmemBytes = v->smem;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -494,7 +495,7 @@ xf_status xf_gemm_run(xf_plan* plan, void* stream) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(plan->grid, 1, 1);
-  cfg.blockDim = dim3(256, 1, 1);
+  cfg.blockDim = dim3(384, 1, 1);
   cfg.dynamicSmemBytes = plan->variant->smem;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr;

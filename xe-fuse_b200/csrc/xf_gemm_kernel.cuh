@@ -46,8 +46,11 @@ struct TileCfg {
   static constexpr int B_BYTES = NGRP * GRP_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BUF_BYTES = 2048;           // 32 rows x 64 B
-  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
-  static constexpr int VEC_BYTES = 4 * 2 * BN * 4;     // {col_scale, bias} per epilogue warp
+  static constexpr int EPI_WARPS = 8;                  // two per TMEM lane quadrant
+  static constexpr int THREADS = (4 + EPI_WARPS) * 32;
+  static constexpr int EPI_BUFS = 2;                   // staging buffers per epilogue warp
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
+  static constexpr int VEC_BYTES = 0;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_LIMIT = 227 * 1024;
   static constexpr int STAGES_RAW =
@@ -94,6 +97,48 @@ __device__ __forceinline__ float load_vec_elem(const VecArg& v, long long idx) {
   if (v.dtype == DT_BF16)
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(v.ptr)[idx]);
   return reinterpret_cast<const float*>(v.ptr)[idx];
+}
+
+// 32 consecutive elements of a per-column vector starting at column col0 (every lane of a warp
+// reads the same addresses: one L1 transaction per load).  Columns >= n_total read as `fill`.
+__device__ __forceinline__ void load_vec32(const VecArg& a, int l, int col0, int n_total, float fill,
+                                           float (&out)[32]) {
+  if (a.ptr == nullptr) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[i] = a.null_default;
+    return;
+  }
+  const long long off = static_cast<long long>(l) * a.batch_stride + col0;
+  if (a.dtype == DT_BF16) {
+    const __nv_bfloat16* ptr = reinterpret_cast<const __nv_bfloat16*>(a.ptr) + off;
+    if (col0 + 32 <= n_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(ptr) + j);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          out[j * 8 + t * 2 + 0] = __uint_as_float(w[t] << 16);
+          out[j * 8 + t * 2 + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = (col0 + i < n_total) ? __bfloat162float(ptr[i]) : fill;
+    }
+  } else {
+    const float* ptr = reinterpret_cast<const float*>(a.ptr) + off;
+    if (col0 + 32 <= n_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(ptr) + j);
+        out[j * 4 + 0] = f.x; out[j * 4 + 1] = f.y; out[j * 4 + 2] = f.z; out[j * 4 + 3] = f.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = (col0 + i < n_total) ? ptr[i] : fill;
+    }
+  }
 }
 
 __device__ __forceinline__ float unary_apply(int op, float x) {
@@ -183,8 +228,7 @@ __device__ __forceinline__ void store_bf16_row(__nv_bfloat16* ptr, const uint32_
 template <int KIND>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const uint32_t (&r)[32],
                                                float (&v)[32], int row, bool row_ok, int l,
-                                               int gcol0, int tcol0, float rs, const float* cvec,
-                                               const float* bvec) {
+                                               int gcol0, float rs) {
 #pragma unroll
   for (int i = 0; i < 32; ++i)
     v[i] = (KIND == 0) ? __uint_as_float(r[i]) : static_cast<float>(static_cast<int>(r[i]));
@@ -209,34 +253,51 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
     for (int i = 0; i < 32; ++i) v[i] *= rs;
   }
   if (e.col_scale.enabled) {
+    float t[32];
+    load_vec32(e.col_scale, l, gcol0, N, 1.0f, t);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= cvec[tcol0 + i];
+    for (int i = 0; i < 32; ++i) v[i] *= t[i];
   }
   if (e.bias.enabled) {
+    float t[32];
+    load_vec32(e.bias, l, gcol0, N, 0.0f, t);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] += bvec[tcol0 + i];
+    for (int i = 0; i < 32; ++i) v[i] += t[i];
   }
-  if (e.unary != UN_NONE) {
-    const int op = e.unary;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = unary_apply(op, v[i]);
+  // The op switches sit OUTSIDE the element loops: every loop body is straight-line code, so the
+  // 32 independent elements of a chunk interleave instead of running as one dependent chain each.
+  switch (e.unary) {
+    case UN_NONE: break;
+#define XF_UNARY_CASE(OP)                                      \
+    case OP:                                                   \
+      _Pragma("unroll") for (int i = 0; i < 32; ++i) v[i] = unary_apply(OP, v[i]); \
+      break;
+    XF_UNARY_CASE(UN_GELU)
+    XF_UNARY_CASE(UN_GELU_TANH)
+    XF_UNARY_CASE(UN_SILU)
+    XF_UNARY_CASE(UN_RELU)
+    XF_UNARY_CASE(UN_SIGMOID)
+    XF_UNARY_CASE(UN_EXP)
+#undef XF_UNARY_CASE
+    default: break;
   }
   if (e.pair == PAIR_SWIGLU || e.pair == PAIR_GEGLU) {
-    const bool ge = (e.pair == PAIR_GEGLU);
-    const bool compact = e.compact != 0;
+    float o[16];
+    if (e.pair == PAIR_SWIGLU) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float g = v[2 * j], u = v[2 * j + 1];
-      float a;
-      if (ge) a = g * 0.5f * (1.0f + erff(g * 0.7071067811865475f));
-      else a = __fdividef(g, 1.0f + __expf(-g));
-      const float o = a * u;
-      if (compact) {
-        v[j] = o;  // j <= 2j: never clobbers an unread input
-      } else {
-        v[2 * j] = o;
-        v[2 * j + 1] = o;
-      }
+      for (int j = 0; j < 16; ++j)
+        o[j] = __fdividef(v[2 * j], 1.0f + __expf(-v[2 * j])) * v[2 * j + 1];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        o[j] = v[2 * j] * 0.5f * (1.0f + erff(v[2 * j] * 0.7071067811865475f)) * v[2 * j + 1];
+    }
+    if (e.compact) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = o[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { v[2 * j] = o[j]; v[2 * j + 1] = o[j]; }
     }
   } else if (e.pair == PAIR_ROPE) {
     float cs[32];
@@ -266,7 +327,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
 }
 
 template <int KIND, int BN, int CTAS, int KS>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   using C = TileCfg<KIND, BN, CTAS, KS>;
   constexpr int STAGES = C::STAGES;
@@ -305,7 +366,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(ptx::smem_u32(&tfull_bar[b]), 1);
-      ptx::mbar_init(ptx::smem_u32(&tempty_bar[b]), 4 * CTAS);
+      ptx::mbar_init(ptx::smem_u32(&tempty_bar[b]), C::EPI_WARPS * CTAS);
     }
     ptx::fence_mbar_init();
   }
@@ -418,13 +479,18 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       }
     }
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    // ------------------------------------------------------------------ epilogue (8 warps)
+    // Two warps share each TMEM lane quadrant and take alternate 32-output-column units of the
+    // tile, so every scheduler of the SM holds two epilogue warps whose latencies overlap.
+    const int ew = warp - 4;
+    const int q = ew & 3;                   // TMEM lane quadrant this warp may read
+    const int half = ew >> 2;               // which of the two warps of the quadrant
     const EpiParams& e = p.epi;
-    uint8_t* stg = epi_base + q * (2 * C::EPI_BUF_BYTES);
+    uint8_t* stg = epi_base + ew * (C::EPI_BUFS * C::EPI_BUF_BYTES);
     int sidx = 0;
     const bool compact = e.compact != 0;
     const int n_out = compact ? (p.N >> 1) : p.N;
+    const int slices_per_unit = compact ? 2 : 1;   // 32 output columns = 1 or 2 accumulator slices
     const uint32_t tempty_leader =
         (CTAS == 2) ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0) : ptx::smem_u32(&tempty_bar[0]);
     int it = 0;
@@ -436,25 +502,6 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       const int l = tc.l;
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      // Per-column vectors of this tile, staged once per warp (no cross-warp synchronisation).
-      float* cvec = vec_base + q * (2 * BN);
-      float* bvec = cvec + BN;
-      if (e.col_scale.enabled || e.bias.enabled) {
-        __syncwarp();
-        for (int i = lane; i < BN; i += 32) {
-          const int n = n0 + i;
-          float cs = 1.0f, bs = 0.0f;
-          if (n < p.N) {
-            if (e.col_scale.enabled)
-              cs = load_vec_elem(e.col_scale, static_cast<long long>(l) * e.col_scale.batch_stride + n);
-            if (e.bias.enabled)
-              bs = load_vec_elem(e.bias, static_cast<long long>(l) * e.bias.batch_stride + n);
-          }
-          cvec[i] = cs;
-          bvec[i] = bs;
-        }
-        __syncwarp();
-      }
       float rs = 1.0f;
       if (e.row_scale.enabled && row_ok)
         rs = load_vec_elem(e.row_scale, static_cast<long long>(l) * e.row_scale.batch_stride + row);
@@ -469,84 +516,87 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
                              (static_cast<uint32_t>(q * 32) << 16);
       const int ncols_tile = min(BN, p.N - n0);           // valid accumulator columns
       const bool warp_rows_ok = (m0 + q * 32) < p.M;      // any row of this warp inside M
-      const int acc_per_chunk = compact ? 64 : 32;
-      const int nchunks = (ncols_tile + acc_per_chunk - 1) / acc_per_chunk;
+      const int nsub = (ncols_tile + 31) / 32;            // 32-column accumulator slices
+      const int nunits = (nsub + slices_per_unit - 1) / slices_per_unit;
+      bool released = false;
+      auto release_tmem = [&]() {   // this warp has read its last slice of the accumulator buffer
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
+        released = true;
+      };
 
-      for (int c = 0; c < nchunks; ++c) {
+      for (int u = half; u < nunits; u += 2) {
         uint32_t pk[16];
-        float v[32];
-        uint32_t r[32];
-        const int tcol0 = c * acc_per_chunk;
-        ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
-        ptx::tmem_ld_wait();
-        if (!compact && c == nchunks - 1) {
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
-        }
-        if (p.d_dtype == DT_S32) {
-          // raw int32 accumulator, no epilogue steps (checked on the host)
-          if (row_ok) {
-            int* dp = reinterpret_cast<int*>(p.D) + static_cast<long long>(l) * p.batch_d +
-                      static_cast<long long>(row) * p.ldd + n0 + tcol0;
-            const int nv = p.N - (n0 + tcol0);
-            if (nv >= 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<uint4*>(dp)[j] =
-                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < nv) dp[i] = static_cast<int>(r[i]);
-            }
-          }
-          continue;
-        }
-        epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, tcol0, rs, cvec, bvec);
-        if (p.d_dtype == DT_F32) {
-          if (row_ok) {
-            float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(l) * p.batch_d +
+        const bool last_unit = (u + 2 >= nunits);
+        int out_col0 = 0;
+        bool stored_direct = false;
+#pragma unroll 1
+        for (int h = 0; h < slices_per_unit; ++h) {
+          const int s = u * slices_per_unit + h;
+          if (s >= nsub) break;   // odd slice count at the N edge of a compact tile
+          float v[32];
+          uint32_t r[32];
+          const int tcol0 = s * 32;
+          ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
+          ptx::tmem_ld_wait();
+          if (last_unit && (h + 1 == slices_per_unit || s + 1 >= nsub)) release_tmem();
+          if (p.diag & 4) { stored_direct = true; continue; }  // diagnostics: TMEM drain only
+          if (p.d_dtype == DT_S32) {
+            // raw int32 accumulator, no epilogue steps (checked on the host)
+            if (row_ok) {
+              int* dp = reinterpret_cast<int*>(p.D) + static_cast<long long>(l) * p.batch_d +
                         static_cast<long long>(row) * p.ldd + n0 + tcol0;
-            const int nv = p.N - (n0 + tcol0);
-            if (nv >= 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
+              const int nv = p.N - (n0 + tcol0);
+              if (nv >= 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<float4*>(dp)[j] =
-                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            } else {
+                for (int j = 0; j < 8; ++j)
+                  reinterpret_cast<uint4*>(dp)[j] =
+                      make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+              } else {
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < nv) dp[i] = v[i];
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) dp[i] = static_cast<int>(r[i]);
+              }
             }
+            stored_direct = true;
+            continue;
           }
-          continue;
+          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs);
+          if (p.d_dtype == DT_F32) {
+            if (row_ok) {
+              float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(l) * p.batch_d +
+                          static_cast<long long>(row) * p.ldd + n0 + tcol0;
+              const int nv = p.N - (n0 + tcol0);
+              if (nv >= 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  reinterpret_cast<float4*>(dp)[j] =
+                      make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) dp[i] = v[i];
+              }
+            }
+            stored_direct = true;
+            continue;
+          }
+          if (!compact) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+            out_col0 = n0 + tcol0;
+          } else if (h == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+            out_col0 = (n0 + tcol0) >> 1;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pk[8 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+          }
         }
-        // bf16 output: 32 output columns per chunk
-        int out_col0;
-        if (!compact) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-          out_col0 = n0 + tcol0;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-          // second half of the 64 accumulator columns
-          if (tcol0 + 32 < ncols_tile) {
-            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0 + 32), r);
-            ptx::tmem_ld_wait();
-          }
-          if (c == nchunks - 1) {
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
-          }
-          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0 + 32, tcol0 + 32, rs, cvec,
-                               bvec);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) pk[8 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-          out_col0 = (n0 + tcol0) >> 1;
-        }
+        if (stored_direct || (p.diag & 8)) continue;
+        // bf16 output: 32 output columns (64 bytes per row) per store
         if (p.direct_store) {
           if (row_ok) {
             __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) +
@@ -561,7 +611,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         } else if (warp_rows_ok) {
-          if (lane == 0) ptx::tma_store_wait_read<1>();  // the buffer used two stores ago is free
+          if (lane == 0) ptx::tma_store_wait_read<C::EPI_BUFS - 1>();  // oldest staging buffer is free
           __syncwarp();
           uint8_t* sbuf = stg + sidx * C::EPI_BUF_BYTES;
           const int sw = (lane >> 1) & 3;  // 64-B swizzle: 16-B chunk index ^= address bits [7,9)
@@ -578,13 +628,10 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
               ptx::tma_store_3d(&p.tm_d_peer[c], ptx::smem_u32(sbuf), out_col0, m0 + q * 32, l);
             ptx::tma_store_commit();
           }
-          sidx ^= 1;
+          sidx = (sidx + 1 == C::EPI_BUFS) ? 0 : sidx + 1;
         }
       }
-      if (nchunks == 0) {  // cannot happen for a scheduled tile, kept so the barrier protocol is total
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
-      }
+      if (!released) release_tmem();   // this warp had no unit in the tile (narrow tile at the N edge)
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();
   }
