@@ -42,9 +42,9 @@ __device__ __forceinline__ float act(int op, float x) {
       float x3 = x * x * x;
       return x * 0.5f * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x3)));
     }
-    case UN_SILU: return x / (1.0f + __expf(-x));
+    case UN_SILU: return __fdividef(x, 1.0f + __expf(-x));
     case UN_RELU: return x > 0.0f ? x : 0.0f;
-    case UN_SIGMOID: return 1.0f / (1.0f + __expf(-x));
+    case UN_SIGMOID: return __fdividef(1.0f, 1.0f + __expf(-x));
     case UN_EXP: return __expf(x);
     default: return x;
   }
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(256) elementwise_kernel(const Args a) {
 #pragma unroll
       for (int j = 0; j < VEC / 2; ++j) {
         const float g = v[2 * j], u = v[2 * j + 1];
-        const float o = (OP == OP_SWIGLU ? g / (1.0f + __expf(-g))
+        const float o = (OP == OP_SWIGLU ? __fdividef(g, 1.0f + __expf(-g))
                                          : g * 0.5f * (1.0f + erff(g * 0.7071067811865475f))) * u;
         v[2 * j] = o;
         v[2 * j + 1] = o;
@@ -298,6 +298,72 @@ __global__ void __launch_bounds__(256) rstd_kernel(const __nv_bfloat16* __restri
   }
 }
 
+// RMS-normalise + absmax-quantise with ONE pass over HBM: the row is staged in shared memory as it
+// is read (16-byte loads), the two reductions and the quantisation then run from shared memory and
+// the int8 row is written with 16-byte stores.  Needs N % 16 == 0 and a row that fits shared memory.
+__global__ void __launch_bounds__(256) rstd_quant_smem_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              float* __restrict__ scale_out,
+                                                              int8_t* __restrict__ xq, long long rows,
+                                                              int N, float eps) {
+  extern __shared__ __align__(16) unsigned char row_smem[];
+  __shared__ float red[8];
+  uint4* srow = reinterpret_cast<uint4*>(row_smem);
+  const int nvec = N / 8;  // 8 bf16 per 16-byte vector
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * N);
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < nvec; i += 256) {
+      const uint4 u = xr[i];
+      srow[i] = u;
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float a = __uint_as_float(w[t] << 16), b = __uint_as_float(w[t] & 0xFFFF0000u);
+        ss += a * a + b * b;
+      }
+    }
+    ss = block_reduce<false>(ss, red);   // also orders the shared-memory writes before the reads below
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
+    float mx = 0.0f;
+    for (int i = threadIdx.x; i < nvec; i += 256) {
+      const uint4 u = srow[i];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        mx = fmaxf(mx, fabsf(__uint_as_float(w[t] << 16) * rstd));
+        mx = fmaxf(mx, fabsf(__uint_as_float(w[t] & 0xFFFF0000u) * rstd));
+      }
+    }
+    mx = block_reduce<true>(mx, red);
+    const float scale = mx / 127.0f + 1e-8f;
+    uint4* qr = reinterpret_cast<uint4*>(xq + row * N);
+    for (int i = threadIdx.x; i < nvec / 2; i += 256) {   // 16 int8 per 16-byte store
+      uint32_t o[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4 u = srow[2 * i + h];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; t += 2) {
+          float f[4] = {__uint_as_float(w[t] << 16), __uint_as_float(w[t] & 0xFFFF0000u),
+                        __uint_as_float(w[t + 1] << 16), __uint_as_float(w[t + 1] & 0xFFFF0000u)};
+          uint32_t packed = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float qv = roundf(__fdividef(f[k] * rstd, scale));   // half away from zero
+            qv = fminf(fmaxf(qv, -128.0f), 127.0f);
+            packed |= (static_cast<uint32_t>(static_cast<int>(qv)) & 0xFFu) << (8 * k);
+          }
+          o[h * 2 + t / 2] = packed;
+        }
+      }
+      qr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    if (threadIdx.x == 0) scale_out[row] = scale;
+    __syncthreads();  // the next row overwrites the staged one
+  }
+}
+
 }  // namespace sa
 }  // namespace xf
 
@@ -411,7 +477,16 @@ static xf_status launch_rstd(const void* x, float* out, int8_t* xq, int M, int N
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   long long grid = rows < static_cast<long long>(sms) * 8 ? rows : static_cast<long long>(sms) * 8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (xq)
+  const size_t row_bytes = static_cast<size_t>(N) * 2;
+  const bool one_pass = xq && (N % 16 == 0) && row_bytes <= 96 * 1024 &&
+                        (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15) == 0;
+  if (one_pass) {
+    if (row_bytes > 48 * 1024)
+      cudaFuncSetAttribute(xf::sa::rstd_quant_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(row_bytes));
+    xf::sa::rstd_quant_smem_kernel<<<static_cast<int>(grid), 256, row_bytes, st>>>(
+        static_cast<const __nv_bfloat16*>(x), out, xq, rows, N, eps);
+  } else if (xq)
     xf::sa::rstd_kernel<true><<<static_cast<int>(grid), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(x), out, xq, rows, N, eps);
   else
