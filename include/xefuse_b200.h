@@ -159,6 +159,11 @@ typedef struct xf_gemm_desc {
    * from the epilogue.  With pointers into the other GPUs' gathered buffers (peer-mapped memory)
    * this is the all-gather of column shards, overlapped with the GEMM instead of following it. */
   void* D_peer[7];
+  /* Size of the workspace that will be handed to xf_gemm_plan_create.  The plan cuts the tiles of
+   * the last wave into K slices only if this covers what xf_gemm_workspace_size reports for the
+   * same descriptor; with less (0 included) it runs whole tiles and uses the first 16 bytes only,
+   * so a caller that never sets it stays correct.  xf_gemm_workspace_size ignores the field. */
+  uint64_t workspace_bytes;
 } xf_gemm_desc;
 
 /* flags */
@@ -169,6 +174,7 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_FORCE_BN256  16  /* use the 256-column CTA tile */
 #define XF_FLAG_FORCE_KS1    32  /* one 128-byte K slab per pipeline stage */
 #define XF_FLAG_FORCE_KS2    64  /* two 128-byte K slabs per pipeline stage */
+#define XF_FLAG_NO_SPLIT     128 /* never cut the tiles of the last, partly filled wave into K slices */
 #define XF_FLAG_DIAG_NO_LOAD  256 /* timing diagnostics only: skip the TMA operand loads (D is garbage) */
 #define XF_FLAG_DIAG_NO_MMA   512 /* timing diagnostics only: skip the tensor-core MMAs (D is garbage) */
 #define XF_FLAG_DIAG_NO_EPILOGUE 1024 /* timing diagnostics only: drain TMEM, compute and store nothing */
@@ -177,7 +183,10 @@ typedef struct xf_plan xf_plan;
 
 /* Checks a problem without touching the GPU.  Returns XF_SUCCESS or the reason it is refused. */
 XF_API xf_status xf_gemm_can_implement(const xf_gemm_desc* desc);
-/* Bytes of caller-owned workspace xf_gemm_plan_create needs (currently a 16-byte status word). */
+/* Bytes of caller-owned device workspace xf_gemm_plan_create needs on the CURRENT device: a
+ * 16-byte status word, plus, when the tiles of the last wave are cut into K slices, counters and
+ * fp32/int32 partial accumulators (a few MB).  Query it on the device the plan will run on, with
+ * the descriptor (flags included) the plan will be created from. */
 XF_API xf_status xf_gemm_workspace_size(const xf_gemm_desc* desc, size_t* bytes);
 /* Copies the descriptor, picks a kernel, encodes TMA tensor maps.  workspace may be NULL when
  * xf_gemm_workspace_size reported 0; otherwise it must stay valid for the plan's lifetime. */

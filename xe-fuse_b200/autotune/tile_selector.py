@@ -5,7 +5,8 @@
 autotune/tile_selector.py:48, so generate_kernel.py / generate_pipeline.py can import this module
 in its place.  On B200 the TileShape of a kernel is only a hint: the library maps it to a native
 CTA tile.  `native_tile()` mirrors that choice (select_variant in csrc/xf_gemm.cu): the cost of a
-variant is waves x tile area / measured efficiency, over the compiled variants
+variant is waves x tile area / measured efficiency, over the compiled variants; the tiles of a
+partly filled last wave are cut into K slices (split_factor), which shortens that wave
 
     (columns, CTAs per tile, 128-byte K slabs per stage): rows = 128 x CTAs
 
@@ -22,24 +23,57 @@ S8_VARIANTS = [((256, 2, 1), 0.91), ((256, 2, 2), 1.00), ((256, 1, 1), 0.84), ((
                ((128, 1, 2), 0.72)]
 
 
-def native_tile(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT):
-    """(rows, columns, ctas, k_elements_per_stage) of the kernel variant the library picks."""
-    best, best_cost = None, None
-    for (bn, ctas, ks), eff in (S8_VARIANTS if dtype in ("s8", "int8") else BF16_VARIANTS):
+MAX_SPLIT, MIN_KB_PER_SLICE = 8, 4
+
+
+def tile_time_us(bn, eff, K, es):
+    """Microseconds one scheduling unit spends on one tile (tile_time_us in csrc/xf_gemm.cu)."""
+    return (2.0 + 0.0029 * K * es) * (bn / 256.0) / eff
+
+
+def split_overhead_us(bn):
+    return 10.0 if bn == 256 else 7.0
+
+
+def split_factor(tiles, units, K, es, bn, ks, eff, compact=False):
+    """K slices per tile of the remainder wave (0 = whole tiles); split_factor in csrc/xf_gemm.cu."""
+    rem = tiles % units
+    if rem == 0:
+        return 0
+    num_kb = ceil(K / ((128 // es) * ks))
+    s = min(units // rem, num_kb // MIN_KB_PER_SLICE, MAX_SPLIT, bn // (64 if compact else 32))
+    if s < 2:
+        return 0
+    return s if tile_time_us(bn, eff, K, es) * (1.0 - 1.0 / s) > split_overhead_us(bn) else 0
+
+
+def native_tile(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT, compact=False, with_split=False):
+    """(rows, columns, ctas, k_elements_per_stage) of the kernel variant the library picks; with
+    with_split also the number of K slices the tiles of the remainder wave are cut into."""
+    best, best_cost, best_split = None, None, 0
+    es = 1 if dtype in ("s8", "int8") else 2
+    for (bn, ctas, ks), eff in (S8_VARIANTS if es == 1 else BF16_VARIANTS):
         tiles = ceil(M / (128 * ctas)) * ceil(N / bn) * L
-        waves = ceil(tiles / (sm_count // ctas))
-        cost = waves * 128.0 * bn / eff
+        units = sm_count // ctas
+        split = split_factor(tiles, units, K, es, bn, ks, eff, compact)
+        t = tile_time_us(bn, eff, K, es)
+        cost = (tiles // units) * t
+        if tiles % units:
+            cost += (t / split + split_overhead_us(bn)) if split else t
         if best is None or cost < best_cost * 0.999:
-            best, best_cost = (bn, ctas, ks), cost
+            best, best_cost, best_split = (bn, ctas, ks), cost, split
     bn, ctas, ks = best
-    kslab = 128 if dtype in ("s8", "int8") else 64
+    kslab = 128 // es
+    if with_split:
+        return 128 * ctas, bn, ctas, ks * kslab, best_split
     return 128 * ctas, bn, ctas, ks * kslab
 
 
-def kernel_name(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT):
+def kernel_name(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT, compact=False):
     """Name the library reports for that variant (xf_gemm_plan_kernel_name without the stage count)."""
-    rows, bn, ctas, kstage = native_tile(M, N, K, dtype, L, sm_count)
-    return f"{'s8' if dtype in ('s8', 'int8') else 'bf16'}_{rows}x{bn}_cta{ctas}_k{kstage}"
+    rows, bn, ctas, kstage, split = native_tile(M, N, K, dtype, L, sm_count, compact, with_split=True)
+    name = f"{'s8' if dtype in ('s8', 'int8') else 'bf16'}_{rows}x{bn}_cta{ctas}_k{kstage}"
+    return name + (f"_ksplit{split}" if split else "")
 
 
 def select_tile(M: int, N: int, K: int, kernel: str = "bare", groups: int = 1) -> str:

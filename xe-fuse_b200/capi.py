@@ -17,6 +17,7 @@ PAIR = {"none": 0, "swiglu": 1, "geglu": 2, "rope": 3, "swap": 4}
 OUT_FULL, OUT_COMPACT = 0, 1
 FLAG_DIRECT_STORE, FLAG_FORCE_1CTA, FLAG_FORCE_2CTA, FLAG_FORCE_BN128, FLAG_FORCE_BN256 = 1, 2, 4, 8, 16
 FLAG_FORCE_KS1, FLAG_FORCE_KS2 = 32, 64
+FLAG_NO_SPLIT = 128
 FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA = 256, 512
 
 STATUS_NAMES = ["XF_SUCCESS", "XF_ERR_MISALIGNED_OPERAND", "XF_ERR_INVALID_DATA_TYPE",
@@ -57,7 +58,7 @@ class XfGemmDesc(C.Structure):
                 ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
                 ("flags", C.c_int32), ("epi", XfEpilogueDesc),
                 ("a_k_slab", C.c_int32), ("num_d_peer", C.c_int32), ("a_k_slab_stride", C.c_int64),
-                ("D_peer", C.c_void_p * 7)]
+                ("D_peer", C.c_void_p * 7), ("workspace_bytes", C.c_uint64)]
 
 
 # Every symbol include/xefuse_b200.h declares (checked by the CPU test-suite).
@@ -196,6 +197,7 @@ class GemmPlan:
         ws = C.c_size_t(0)
         check(L_.xf_gemm_workspace_size(C.byref(d), C.byref(ws)))
         self.workspace = torch.zeros(max(int(ws.value), 16), dtype=torch.uint8, device=A.device)
+        d.workspace_bytes = self.workspace.numel()
         self.handle = C.c_void_p()
         check(L_.xf_gemm_plan_create(C.byref(d), self.workspace.data_ptr(), C.byref(self.handle)))
         self.kernel_name = L_.xf_gemm_plan_kernel_name(self.handle).decode()

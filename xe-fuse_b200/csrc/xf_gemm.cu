@@ -285,11 +285,53 @@ static MatArg to_mat(const xf_mat& m) {
 
 static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Measured throughput of each variant on a large bf16 problem (4096 x 28672 x 4096 on B200),
+// relative to the paired 256x256 tile with 128-element K stages.  Narrow tiles and short stages
+// pay the per-stage barrier hand-off more often and re-read operands from L2 more.
+static double variant_eff(const Variant& v) {
+  if (v.bn == 256) return v.ctas == 2 ? (v.ks == 2 ? 1.00 : 0.91) : 0.84;
+  return v.ctas == 2 ? (v.ks == 2 ? 0.67 : 0.48) : (v.ks == 2 ? 0.72 : 0.55);
+}
+
+// Time one scheduling unit spends on one tile, in microseconds: a fixed part (pipeline fill, the
+// exposed end of the epilogue) plus the K loop, fitted to 256x256 tiles at K = 4096 and 14336 bf16
+// (26 and 85 us at the clocks the part sustains under load).
+static double tile_time_us(const Variant& v, int K, int es) {
+  return (2.0 + 0.0029 * K * es) * (v.bn / 256.0) / variant_eff(v);
+}
+
+// Split-K of the remainder wave.  With T tiles on U scheduling units, the last wave holds
+// T % U tiles and leaves the other units idle; cutting each of those tiles into S K slices fills
+// S times as many units for 1/S of the time, at the price of passing the partial accumulators
+// through L2 (publish, wait for the other slices, sum: about 10 us for a 256-column tile).
+// Returns S, or 0 for whole tiles.
+static const int kMaxSplit = 8;
+static const int kMinKbPerSlice = 4;
+static double split_overhead_us(const Variant& v) { return v.bn == 256 ? 10.0 : 7.0; }
+static int split_factor(const Variant& v, const xf_gemm_desc* d, int tiles, int units) {
+  if (d->flags & XF_FLAG_NO_SPLIT) return 0;
+  if (units <= 0) return 0;
+  const int rem = tiles % units;
+  if (rem == 0) return 0;
+  const int es = d->dtype_ab == XF_DT_BF16 ? 2 : 1;
+  const int num_kb = ceil_div(d->K, (128 / es) * v.ks);
+  int s = units / rem;
+  if (s > num_kb / kMinKbPerSlice) s = num_kb / kMinKbPerSlice;
+  if (s > kMaxSplit) s = kMaxSplit;
+  // every slice finishes whole 32-output-column units of the tile
+  const int units_per_tile = v.bn / (d->epi.out_layout == XF_OUT_COMPACT ? 64 : 32);
+  if (s > units_per_tile) s = units_per_tile;
+  if (s < 2) return 0;
+  const double t = tile_time_us(v, d->K, es);
+  return t * (1.0 - 1.0 / s) > split_overhead_us(v) ? s : 0;
+}
+
 // Picks the CTA tile.  The caller's TileShape (an Intel Xe work-group tile) is only a hint; the
-// native tiles are {128,256} rows x {128,256} columns.  The estimate is waves x tile cost, with a
-// mild preference for the paired-CTA 256x256 tile, which halves shared-memory traffic for B.
+// native tiles are {128,256} rows x {128,256} columns.  The estimate is whole waves x tile time
+// plus the remainder wave, whole or split.
 static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
   const int kind = d->dtype_ab == XF_DT_BF16 ? 0 : 1;
+  const int es = kind == 0 ? 2 : 1;
   const Variant* best = nullptr;
   double best_cost = 0;
   for (int i = 0; i < g_num_variants; ++i) {
@@ -303,15 +345,10 @@ static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
     if ((d->flags & XF_FLAG_FORCE_KS2) && v.ks != 2) continue;
     const int tiles = ceil_div(d->M, 128 * v.ctas) * ceil_div(d->N, v.bn) * d->L;
     const int units = sm_count / v.ctas;
-    const int waves = ceil_div(tiles, units);
-    // Measured throughput of each variant on a large bf16 problem (4096 x 28672 x 4096 on B200),
-    // relative to the paired 256x256 tile with 128-element K stages.  Narrow tiles and short
-    // stages pay the per-stage barrier hand-off more often and re-read operands from L2 more.
-    double eff;
-    if (v.bn == 256) eff = v.ctas == 2 ? (v.ks == 2 ? 1.00 : 0.91) : 0.84;
-    else eff = v.ctas == 2 ? (v.ks == 2 ? 0.67 : 0.48) : (v.ks == 2 ? 0.72 : 0.55);
-    double tile_work = 128.0 * v.bn;  // per SM
-    double cost = waves * tile_work / eff;
+    const int split = split_factor(v, d, tiles, units);
+    const double t = tile_time_us(v, d->K, es);
+    double cost = (tiles / units) * t;
+    if (tiles % units) cost += split ? t / split + split_overhead_us(v) : t;
     if (!best || cost < best_cost * 0.999) {
       best = &v;
       best_cost = cost;
@@ -320,8 +357,20 @@ static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
   return best;
 }
 
-static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* plan,
-                            bool clear_status_now = true) {
+// What the schedule of one problem looks like on the current device: the tile variant, how many
+// scheduling units (CTAs or CTA pairs) run at once, and the split of the remainder wave with the
+// workspace it needs.  Workspace layout: [0,16) status word, [256, ...) split counters, then the
+// partial accumulators (256-byte aligned).
+struct Geometry {
+  const Variant* v;
+  int dev, sm_count, units;
+  int total_tiles, num_kb;
+  int split_s, split_tiles;
+  size_t counters_off, partials_off, workspace_bytes;
+};
+
+static xf_status plan_geometry(const xf_gemm_desc* d, Geometry* g) {
+  memset(g, 0, sizeof(*g));
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) {
     set_error("no CUDA device: %s", cudaGetErrorString(cudaGetLastError()));
@@ -339,6 +388,61 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
     set_error("no kernel variant matches the requested flags");
     return XF_ERR_NOT_SUPPORTED;
   }
+  g->v = v; g->dev = dev; g->sm_count = sm_count;
+  cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(v->fn),
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem);
+  if (ce != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(smem=%d) failed: %s", v->smem, cudaGetErrorString(ce));
+    return XF_ERR_INTERNAL;
+  }
+  const int es = elem_size(d->dtype_ab);
+  g->num_kb = ceil_div(d->K, (128 / es) * v->ks);
+  g->total_tiles = ceil_div(d->M, 128 * v->ctas) * ceil_div(d->N, v->bn) * d->L;
+  int units = sm_count / v->ctas;
+  if (v->ctas == 2) {
+    // number of CTA pairs that can be co-resident (GPC boundaries may leave an SM unpaired)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count - (sm_count & 1), 1, 1);
+    cfg.blockDim = dim3(384, 1, 1);
+    cfg.dynamicSmemBytes = v->smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int nclusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&nclusters, reinterpret_cast<const void*>(v->fn), &cfg) ==
+            cudaSuccess && nclusters > 0)
+      units = nclusters;
+    else
+      cudaGetLastError();
+  }
+  g->units = units;
+  g->split_s = split_factor(*v, d, g->total_tiles, units);
+  g->split_tiles = g->split_s ? g->total_tiles % units : 0;
+  g->counters_off = 256;
+  const size_t counters = static_cast<size_t>(g->split_tiles) * v->ctas * 8 * sizeof(int);
+  g->partials_off = g->counters_off + ((counters + 255) & ~static_cast<size_t>(255));
+  const size_t partials = static_cast<size_t>(g->split_tiles) * g->split_s * v->ctas * 128 * v->bn * 4;
+  g->workspace_bytes = g->split_s ? g->partials_off + partials : 16;
+  return XF_SUCCESS;
+}
+
+static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* plan,
+                            bool clear_status_now = true) {
+  Geometry g;
+  xf_status gs = plan_geometry(d, &g);
+  if (gs != XF_SUCCESS) return gs;
+  if (g.split_s && (!workspace || d->workspace_bytes < g.workspace_bytes || !aligned16(workspace))) {
+    // the caller did not promise room for the partial accumulators: whole tiles only.  The tile
+    // variant may differ from the one a split would have chosen, so select again.
+    xf_gemm_desc whole = *d;
+    whole.flags |= XF_FLAG_NO_SPLIT;
+    gs = plan_geometry(&whole, &g);
+    if (gs != XF_SUCCESS) return gs;
+  }
+  const int dev = g.dev;
+  const Variant* v = g.v;
   plan->variant = v;
   plan->device = dev;
   GemmParams& p = plan->params;
@@ -411,37 +515,24 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
     }
   }
 
-  cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(v->fn),
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem);
-  if (ce != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(smem=%d) failed: %s", v->smem, cudaGetErrorString(ce));
-    return XF_ERR_INTERNAL;
+  const int total_tiles = g.total_tiles;
+  p.split_s = g.split_s;
+  p.split_first = total_tiles - g.split_tiles;
+  p.total_items = p.split_first + g.split_tiles * (g.split_s ? g.split_s : 1);
+  if (g.split_s) {
+    p.split_counters = reinterpret_cast<int*>(static_cast<char*>(workspace) + g.counters_off);
+    p.split_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + g.partials_off);
   }
-  const int total_tiles = p.tiles_m * p.tiles_n * d->L;
-  int units = sm_count / v->ctas;
-  if (v->ctas == 2) {
-    // number of CTA pairs that can be co-resident (GPC boundaries may leave an SM unpaired)
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(sm_count - (sm_count & 1), 1, 1);
-    cfg.blockDim = dim3(384, 1, 1);
-    cfg.dynamicSmemBytes = v->smem;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    int nclusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&nclusters, reinterpret_cast<const void*>(v->fn), &cfg) ==
-            cudaSuccess && nclusters > 0)
-      units = nclusters;
-    else
-      cudaGetLastError();
-  }
-  const int nunits = total_tiles < units ? total_tiles : units;
+  const int nunits = p.total_items < g.units ? p.total_items : g.units;
   plan->grid = nunits * v->ctas;
-  snprintf(plan->name, sizeof(plan->name), "%s_s%d", v->name, v->stages);
+  cudaError_t ce;
+  if (g.split_s)
+    snprintf(plan->name, sizeof(plan->name), "%s_s%d_ksplit%d", v->name, v->stages, g.split_s);
+  else
+    snprintf(plan->name, sizeof(plan->name), "%s_s%d", v->name, v->stages);
   if (p.status && clear_status_now) {
-    ce = cudaMemset(p.status, 0, 16);
+    // the status word, and the split counters: each launch leaves them at zero again
+    ce = cudaMemset(p.status, 0, g.split_s ? g.partials_off : 16);
     if (ce != cudaSuccess) {
       set_error("clearing the workspace status word failed: %s", cudaGetErrorString(ce));
       return XF_ERR_INTERNAL;
@@ -461,8 +552,17 @@ xf_status xf_gemm_workspace_size(const xf_gemm_desc* desc, size_t* bytes) {
     xf::set_error("null output pointer");
     return XF_ERR_INVALID_PROBLEM;
   }
-  (void)desc;
   *bytes = 16;
+  if (!desc || xf::validate(desc) != XF_SUCCESS) return XF_SUCCESS;  // can_implement reports why
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+    cudaGetLastError();
+    return XF_SUCCESS;  // no GPU here: a plan cannot be created either
+  }
+  xf::Geometry g;
+  xf_status s = xf::plan_geometry(desc, &g);
+  if (s != XF_SUCCESS) return s;
+  *bytes = g.workspace_bytes;
   return XF_SUCCESS;
 }
 
@@ -560,9 +660,13 @@ static xf_status static_workspace_address(void** out) {
   return XF_SUCCESS;
 }
 
-xf_status xf_gemm_run_static_workspace(const xf_gemm_desc* desc, void* stream) {
-  xf_status s = xf::validate(desc);
+xf_status xf_gemm_run_static_workspace(const xf_gemm_desc* caller_desc, void* stream) {
+  xf_status s = xf::validate(caller_desc);
   if (s != XF_SUCCESS) return s;
+  // The split of the remainder wave needs megabytes of scratch; this entry runs whole tiles only.
+  xf_gemm_desc local = *caller_desc;
+  local.flags |= XF_FLAG_NO_SPLIT;
+  const xf_gemm_desc* desc = &local;
   size_t need = 0;
   s = xf_gemm_workspace_size(desc, &need);
   if (s != XF_SUCCESS) return s;
@@ -601,6 +705,11 @@ xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code) {
     return XF_ERR_INTERNAL;
   }
   if (*device_code != 0) {
+    // a launch that gave up may have left the split counters part-way: clear them for the next one
+    if (plan->params.split_counters)
+      cudaMemset(plan->params.split_counters, 0,
+                 reinterpret_cast<char*>(plan->params.split_partials) -
+                     reinterpret_cast<char*>(plan->params.split_counters));
     xf::set_error("kernel %s gave up in a bounded wait (device code %d)", plan->name, *device_code);
     return XF_ERR_INTERNAL;
   }

@@ -92,6 +92,26 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile) 
   return c;
 }
 
+// One unit of the persistent schedule: a whole tile, or one K slice of a split tile.
+struct WorkItem {
+  int tile, kb0, kb1, slice, split_idx;   // split_idx < 0: whole tile
+};
+
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int w) {
+  WorkItem it;
+  if (p.split_s == 0 || w < p.split_first) {
+    it.tile = w; it.kb0 = 0; it.kb1 = p.num_kb; it.slice = 0; it.split_idx = -1;
+  } else {
+    const int j = w - p.split_first;
+    it.split_idx = j / p.split_s;
+    it.slice = j - it.split_idx * p.split_s;
+    it.tile = p.split_first + it.split_idx;
+    it.kb0 = static_cast<int>(static_cast<long long>(it.slice) * p.num_kb / p.split_s);
+    it.kb1 = static_cast<int>(static_cast<long long>(it.slice + 1) * p.num_kb / p.split_s);
+  }
+  return it;
+}
+
 __device__ __forceinline__ float load_vec_elem(const VecArg& v, long long idx) {
   if (v.ptr == nullptr) return v.null_default;
   if (v.dtype == DT_BF16)
@@ -351,7 +371,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t cta_rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
   const int cluster_idx = (CTAS == 2) ? static_cast<int>(ptx::cluster_id_x()) : blockIdx.x;
   const int num_clusters = (CTAS == 2) ? static_cast<int>(ptx::num_clusters_x()) : gridDim.x;
-  const int total_tiles = p.tiles_m * p.tiles_n * p.L;
+  const int total_items = p.total_items;
   const long long budget = p.wait_budget;
 
   if (warp == 0 && lane == 0) {
@@ -389,13 +409,14 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cluster_idx; tile < total_tiles && ok; tile += num_clusters) {
-        const TileCoord tc = decode_tile(p, tile);
+      for (int w = cluster_idx; w < total_items && ok; w += num_clusters) {
+        const WorkItem wi = decode_item(p, w);
+        const TileCoord tc = decode_tile(p, wi.tile);
         const int row0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
         const int col0 = tc.tn * BN + static_cast<int>(cta_rank) * C::BN_CTA;
         const int la = p.a_batched ? tc.l : 0;
         const int lb = p.b_batched ? tc.l : 0;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, budget)) {
             if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_PRODUCER_EMPTY);
             ok = false;
@@ -437,7 +458,8 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = cluster_idx; tile < total_tiles && ok; tile += num_clusters, ++it) {
+      for (int w = cluster_idx; w < total_items && ok; w += num_clusters, ++it) {
+        const WorkItem wi = decode_item(p, w);
         const int buf = it & 1;
         if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1u, budget)) {
           if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_MMA_TMEM_EMPTY);
@@ -445,7 +467,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, budget)) {
             if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_MMA_FULL);
             ok = false;
@@ -465,7 +487,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             const int a_off = (k / MMAS_PER_SLAB) * C::A_SLAB_BYTES + (k % MMAS_PER_SLAB) * 32;
             ptx::umma<KIND, CTAS>(d_tmem, adesc + static_cast<uint64_t>(a_off >> 4),
                                   bdesc + static_cast<uint64_t>(k * ((C::UK * 128) >> 4)), idesc,
-                                  (kb | k) != 0 ? 1u : 0u);
+                                  (kb > wi.kb0 || k > 0) ? 1u : 0u);
           }
           const uint32_t eb = ptx::smem_u32(&empty_bar[stage]);
           ptx::umma_commit<CTAS>(eb);
@@ -494,8 +516,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t tempty_leader =
         (CTAS == 2) ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0) : ptx::smem_u32(&tempty_bar[0]);
     int it = 0;
-    for (int tile = cluster_idx; tile < total_tiles; tile += num_clusters, ++it) {
-      const TileCoord tc = decode_tile(p, tile);
+    for (int w = cluster_idx; w < total_items; w += num_clusters, ++it) {
+      const WorkItem wi = decode_item(p, w);
+      const TileCoord tc = decode_tile(p, wi.tile);
       const int buf = it & 1;
       const int m0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
       const int n0 = tc.tn * BN;
@@ -526,7 +549,63 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         released = true;
       };
 
-      for (int u = half; u < nunits; u += 2) {
+      // Split tile.  Every slice publishes its raw accumulator rows, then the S slices share the
+      // finishing work: slice i sums, in slice order, the 32-output-column units u = i (mod S) of
+      // all S partials and runs the epilogue on them.  A slice item is always the last item of
+      // its CTA and all CTAs of the grid are resident, so the wait below cannot deadlock; it is
+      // bounded all the same.
+      const float* part_base = nullptr;   // non-null: accumulators come from the partials, not TMEM
+      int* split_ctr = nullptr;           // [0] warps that have published, [1] warps that are done
+      int u_first = half, u_step = 2;
+      if (wi.split_idx >= 0) {
+        const size_t slab = static_cast<size_t>(C::BM) * BN;   // words per (slice, CTA)
+        // slab layout [32-column slice][16-byte chunk][row]: the 32 lanes of a store are contiguous
+        uint4* mine = reinterpret_cast<uint4*>(
+                          p.split_partials +
+                          ((static_cast<size_t>(wi.split_idx) * p.split_s + wi.slice) * CTAS + cta_rank) * slab) +
+                      (q * 32 + lane);
+        for (int u = half; u < nunits; u += 2) {
+          for (int h = 0; h < slices_per_unit; ++h) {
+            const int s = u * slices_per_unit + h;
+            if (s >= nsub) break;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(s * 32), r);
+            ptx::tmem_ld_wait();
+            uint4* dst = mine + static_cast<size_t>(s) * 8 * C::BM;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              dst[j * C::BM] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          }
+        }
+        release_tmem();
+        __threadfence();
+        __syncwarp();
+        split_ctr = p.split_counters + (wi.split_idx * CTAS + static_cast<int>(cta_rank)) * 8;
+        if (lane == 0) atomicAdd(split_ctr, 1);
+        u_first = wi.slice + p.split_s * half;
+        u_step = 2 * p.split_s;
+        if (u_first < nunits) {
+          int seen_all = 1;
+          if (lane == 0) {
+            const int target = C::EPI_WARPS * p.split_s;
+            const long long t0 = clock64();
+            while (ptx::ld_acquire_gpu(split_ctr) < target) {
+              if (clock64() - t0 > budget) { seen_all = 0; break; }
+              __nanosleep(64);
+            }
+          }
+          seen_all = __shfl_sync(0xffffffffu, seen_all, 0);
+          __threadfence();
+          if (!seen_all) {
+            if (p.status && lane == 0) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_SPLIT_PARTIALS);
+            u_first = nunits;   // nothing to finish; fall through to the bookkeeping
+          }
+        }
+        part_base = p.split_partials + (static_cast<size_t>(wi.split_idx) * p.split_s * CTAS + cta_rank) * slab +
+                    static_cast<size_t>(q * 32 + lane) * 4;
+      }
+
+      for (int u = u_first; u < nunits; u += u_step) {
         uint32_t pk[16];
         const bool last_unit = (u + 2 >= nunits);
         int out_col0 = 0;
@@ -538,9 +617,46 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           float v[32];
           uint32_t r[32];
           const int tcol0 = s * 32;
-          ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
-          ptx::tmem_ld_wait();
-          if (last_unit && (h + 1 == slices_per_unit || s + 1 >= nsub)) release_tmem();
+          if (part_base == nullptr) {
+            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
+            ptx::tmem_ld_wait();
+            if (last_unit && (h + 1 == slices_per_unit || s + 1 >= nsub)) release_tmem();
+          } else {
+            // sum the slices in slice order (the same order whichever slice arrived last); L2 loads:
+            // the partials were written by other SMs
+            const size_t slice_stride = static_cast<size_t>(CTAS) * C::BM * BN;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+            const uint4* src0 = reinterpret_cast<const uint4*>(part_base) + static_cast<size_t>(s) * 8 * C::BM;
+            const size_t slice_stride4 = slice_stride / 4;
+            auto add4 = [&](int j, const uint4& x) {
+              const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                if constexpr (KIND == 0)
+                  r[4 * j + t] = __float_as_uint(__uint_as_float(r[4 * j + t]) + __uint_as_float(xs[t]));
+                else
+                  r[4 * j + t] = static_cast<uint32_t>(static_cast<int>(r[4 * j + t]) + static_cast<int>(xs[t]));
+              }
+            };
+            int sl = 0;
+            for (; sl + 2 <= p.split_s; sl += 2) {   // two slices (16 loads) in flight per lane
+              uint4 x0[8], x1[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                x0[j] = __ldcg(src0 + sl * slice_stride4 + j * C::BM);
+                x1[j] = __ldcg(src0 + (sl + 1) * slice_stride4 + j * C::BM);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) add4(j, x0[j]);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) add4(j, x1[j]);
+            }
+            if (sl < p.split_s) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) add4(j, __ldcg(src0 + sl * slice_stride4 + j * C::BM));
+            }
+          }
           if (p.diag & 4) { stored_direct = true; continue; }  // diagnostics: TMEM drain only
           if (p.d_dtype == DT_S32) {
             // raw int32 accumulator, no epilogue steps (checked on the host)
@@ -632,6 +748,18 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         }
       }
       if (!released) release_tmem();   // this warp had no unit in the tile (narrow tile at the N edge)
+      if (split_ctr != nullptr) {
+        // The last warp of the last slice to get here knows every wait above has ended: it leaves
+        // both counters at zero for the next launch.
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          if (atomicAdd(split_ctr + 1, 1) == C::EPI_WARPS * p.split_s - 1) {
+            split_ctr[0] = 0;
+            split_ctr[1] = 0;
+          }
+        }
+      }
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();
   }

@@ -17,6 +17,7 @@ enum : int {
   DEV_TIMEOUT_MMA_FULL = 2,
   DEV_TIMEOUT_MMA_TMEM_EMPTY = 3,
   DEV_TIMEOUT_EPI_TMEM_FULL = 4,
+  DEV_TIMEOUT_SPLIT_PARTIALS = 5,   // a K slice never saw the other slices' partial accumulators
 };
 
 struct VecArg {
@@ -68,6 +69,16 @@ struct alignas(64) GemmParams {
   int direct_store;        // 1: plain global stores for D
   int diag;                // diagnostics: bit0 skip the TMA loads, bit1 skip the MMAs (results are garbage)
   int* status;             // device status word (may be null)
+  // Split-K of the remainder wave: work items [0, split_first) are whole tiles; the tiles from
+  // split_first on are each cut into split_s K slices, one work item per slice.  Slices publish
+  // raw partial accumulators in split_partials, wait for one another (split_counters), and each
+  // sums, in slice order, its share of the tile's columns and runs the epilogue there.
+  // split_s == 0: no split.
+  int split_first;
+  int split_s;
+  int total_items;
+  int* split_counters;     // [split tiles][CTAS][8]: [0] published, [1] done; zero between launches
+  float* split_partials;   // [split tiles][split_s][CTAS][128][BN] raw accumulator words
   long long wait_budget;   // clock64 cycles a wait may take before giving up
   EpiParams epi;
 };

@@ -715,6 +715,12 @@ class GemmUniversalAdapter {
     Status s = lower(a, ext_, d);
     if (s != Status::kSuccess) return s;
     release();
+    // get_workspace_size() is static and cannot see this object's extensions: only when they leave
+    // the tile choice alone is the caller's workspace known to be the size the plan needs
+    if (workspace != nullptr && ext_.flags == 0) {
+      size_t n = 0;
+      if (xf_gemm_workspace_size(&d, &n) == XF_SUCCESS) d.workspace_bytes = n;
+    }
     s = Status(xf_gemm_plan_create(&d, workspace, &plan_));
     if (s != Status::kSuccess) return s;
     make_resident(d, stream);
