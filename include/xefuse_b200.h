@@ -261,6 +261,40 @@ XF_API xf_status xf_compute_rstd_and_quantize(const void* x, int8_t* xq, float* 
                                               int M, int N, int L, float eps, void* stream);
 
 /*
+ * Engine-style stand-alone passes: the comparison arm of the reference's generated pipelines
+ * (namespace xe_fuse::vllm_equiv, include/xe-fuse/standalone/vllm_ops.hpp).  bf16 data unless
+ * noted, fp32 math, one rounding to bf16.  All asynchronous on `stream`.
+ */
+/* out[m,:] = input[m,:] * rsqrt(mean(input[m,:]^2) + eps) * weight[:]; weight bf16 [N]; out may be
+ * input (vllm_ops.hpp:33-69). */
+XF_API xf_status xf_ve_rms_norm(void* out, const void* input, const void* weight, int M, int N,
+                                float eps, void* stream);
+/* residual += input; input = RMSNorm(residual) * weight, both in place (vllm_ops.hpp:75-114). */
+XF_API xf_status xf_ve_fused_add_rms_norm(void* input, void* residual, const void* weight, int M,
+                                          int N, float eps, void* stream);
+/* out[m,i] = act(input[m,i]) * input[m,d+i]; input [M,2d], out [M,d]; gelu=0 SiLU, 1 erf-GeLU
+ * (silu_and_mul / gelu_and_mul, vllm_ops.hpp:119-164). */
+XF_API xf_status xf_ve_act_and_mul(void* out, const void* input, int d, int M, int gelu,
+                                   void* stream);
+/* NeoX rotary embedding in place on query [M,num_heads,head_size] and, if not null, key
+ * [M,num_kv_heads,head_size]; cos_sin_cache fp32 [M,rot_dim] = cos half then sin half
+ * (vllm_ops.hpp:170-227). */
+XF_API xf_status xf_ve_rotary_embedding(void* query, void* key, const float* cos_sin_cache,
+                                        int head_size, int num_heads, int num_kv_heads, int rot_dim,
+                                        int M, void* stream);
+/* int32 accumulator [L,M,2d] -> bf16 [L,M,2d]: W8A8 dequantisation, act(gate)*up over the two
+ * halves, the result written to both halves (dequant_and_silu_mul / dequant_and_gelu_mul,
+ * vllm_ops.hpp:244-311). */
+XF_API xf_status xf_ve_dequant_act_mul(void* out, const int32_t* acc, const float* scale_token,
+                                       const float* scale_channel, int d, int M, int L, int gelu,
+                                       void* stream);
+/* int32 accumulator [L,M,N] -> bf16: W8A8 dequantisation then the interleaved-pair rotation with a
+ * full fp32 cos_sin [L,M,N] (dequant_and_rotary_embedding, vllm_ops.hpp:317-346). */
+XF_API xf_status xf_ve_dequant_rotary(void* out, const int32_t* acc, const float* scale_token,
+                                      const float* scale_channel, const float* cos_sin, int M, int N,
+                                      int L, void* stream);
+
+/*
  * Harness utilities behind the front end's cutlass/util shims (not on the fused path): the
  * seeded fill the harness mains call initialize_block, the naive device GEMM they use to rebuild
  * the expected accumulator (cutlass::reference::device::GemmComplex in tests/test_k1.cpp:113-117)

@@ -377,3 +377,114 @@ XO_API void xo_rope_table(float* cs, int M, int width, float theta) {
       cs[(size_t)m * width + 2 * i + 1] = sinf(angle);
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Engine-style stand-alone passes (include/xe-fuse/standalone/vllm_ops.hpp), the comparison arm
+ * of the reference's generated pipelines.  Row sums here run in element order in fp32, as one
+ * work-item of the reference would; the device sums the same terms in a tree.
+ * ------------------------------------------------------------------------------------------ */
+
+/* vllm_ops.hpp:33-69: out = bf16(x * rsqrt(mean(x^2) + eps) * weight), weight bf16. */
+XO_API void xo_ve_rms_norm(uint16_t* out, const uint16_t* in, const uint16_t* weight, int M, int N, float eps) {
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    float var = 0.0f;
+    for (int n = 0; n < N; ++n) {
+      float x = bf16_to_f32(in[(size_t)m * N + n]);
+      var += x * x;
+    }
+    const float s = 1.0f / sqrtf(var / (float)N + eps);
+    for (int n = 0; n < N; ++n) {
+      float x = bf16_to_f32(in[(size_t)m * N + n]);
+      out[(size_t)m * N + n] = f32_to_bf16_rne(x * s * bf16_to_f32(weight[n]));
+    }
+  }
+}
+
+/* vllm_ops.hpp:75-114: residual = bf16(input + residual) with the variance over the unrounded
+ * sums; input = bf16(residual * s * weight) from the rounded residual. */
+XO_API void xo_ve_fused_add_rms_norm(uint16_t* input, uint16_t* residual, const uint16_t* weight, int M, int N,
+                                     float eps) {
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    float var = 0.0f;
+    for (int n = 0; n < N; ++n) {
+      const size_t i = (size_t)m * N + n;
+      float sum = bf16_to_f32(input[i]) + bf16_to_f32(residual[i]);
+      var += sum * sum;
+      residual[i] = f32_to_bf16_rne(sum);
+    }
+    const float s = 1.0f / sqrtf(var / (float)N + eps);
+    for (int n = 0; n < N; ++n) {
+      const size_t i = (size_t)m * N + n;
+      input[i] = f32_to_bf16_rne(bf16_to_f32(residual[i]) * s * bf16_to_f32(weight[n]));
+    }
+  }
+}
+
+/* vllm_ops.hpp:119-164: out[m,i] = act(in[m,i]) * in[m,d+i]; gelu != 0 selects erf-GeLU. */
+XO_API void xo_ve_act_and_mul(uint16_t* out, const uint16_t* in, int d, int M, int gelu) {
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m)
+    for (int i = 0; i < d; ++i) {
+      float gate = bf16_to_f32(in[(size_t)m * 2 * d + i]);
+      float up = bf16_to_f32(in[(size_t)m * 2 * d + d + i]);
+      float a = gelu ? gelu_erf(gate) : silu(gate);
+      out[(size_t)m * d + i] = f32_to_bf16_rne(a * up);
+    }
+}
+
+/* vllm_ops.hpp:170-227: NeoX pairs (h[j], h[rot_dim/2+j]) of every head of one [M,heads,head_size]
+ * tensor, cache [M,rot_dim] = cos half | sin half.  Call once for the query and once for the key. */
+XO_API void xo_ve_rotary_neox(uint16_t* data, const float* cache, int head_size, int heads, int rot_dim, int M) {
+  const int embed = rot_dim / 2;
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m)
+    for (int h = 0; h < heads; ++h)
+      for (int j = 0; j < embed; ++j) {
+        uint16_t* base = data + ((size_t)m * heads + h) * head_size;
+        float x = bf16_to_f32(base[j]), y = bf16_to_f32(base[embed + j]);
+        float c = cache[(size_t)m * rot_dim + j], s = cache[(size_t)m * rot_dim + embed + j];
+        base[j] = f32_to_bf16_rne(x * c - y * s);
+        base[embed + j] = f32_to_bf16_rne(y * c + x * s);
+      }
+}
+
+/* vllm_ops.hpp:244-311: rows = L*M; gate/up halves dequantised as (acc*st)*sc, result duplicated. */
+XO_API void xo_ve_dequant_act_mul(uint16_t* out, const int32_t* acc, const float* st, const float* sc, int d, int M,
+                                  int L, int gelu) {
+  const int N = 2 * d;
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < M * L; ++r) {
+    const int l = r / M;
+    for (int i = 0; i < d; ++i) {
+      float gate = (float)acc[(size_t)r * N + i] * st[r] * sc[(size_t)l * N + i];
+      float up = (float)acc[(size_t)r * N + d + i] * st[r] * sc[(size_t)l * N + d + i];
+      uint16_t v = f32_to_bf16_rne((gelu ? gelu_erf(gate) : silu(gate)) * up);
+      out[(size_t)r * N + i] = v;
+      out[(size_t)r * N + d + i] = v;
+    }
+  }
+}
+
+/* vllm_ops.hpp:317-346: dequantise, then rotate the interleaved pairs with cos_sin [L,M,N]; a last
+ * unpaired column is only dequantised. */
+XO_API void xo_ve_dequant_rotary(uint16_t* out, const int32_t* acc, const float* st, const float* sc,
+                                 const float* cos_sin, int M, int N, int L) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < M * L; ++r) {
+    const int l = r / M;
+    const size_t base = (size_t)r * N;
+    for (int e = 0; e < N; e += 2) {
+      float xe = (float)acc[base + e] * st[r] * sc[(size_t)l * N + e];
+      if (e + 1 >= N) {
+        out[base + e] = f32_to_bf16_rne(xe);
+        break;
+      }
+      float xo = (float)acc[base + e + 1] * st[r] * sc[(size_t)l * N + e + 1];
+      float c = cos_sin[base + e], s = cos_sin[base + e + 1];
+      out[base + e] = f32_to_bf16_rne(xe * c + xo * s);
+      out[base + e + 1] = f32_to_bf16_rne(-xe * s + xo * c);
+    }
+  }
+}

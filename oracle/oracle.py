@@ -203,3 +203,59 @@ def quantize_columns_offline(W):
     scale = np.where(scale == 0, 1e-8, scale)
     Wq = np.round(np.clip(W / scale[None, :], -128.0, 127.0)).astype(np.int8)
     return Wq, scale.astype(np.float32)
+
+
+# ---- engine-style stand-alone passes (include/xe-fuse/standalone/vllm_ops.hpp) -------------------
+def ve_rms_norm(x, weight, eps=1e-6):
+    x = np.ascontiguousarray(x, np.uint16)
+    M, N = x.shape
+    out = np.empty_like(x)
+    lib().xo_ve_rms_norm(_p(out), _p(x), _p(np.ascontiguousarray(weight, np.uint16)), M, N, C.c_float(eps))
+    return out
+
+
+def ve_fused_add_rms_norm(x, residual, weight, eps=1e-6):
+    """Returns (normalised input, updated residual)."""
+    x = np.array(x, np.uint16, order="C")
+    r = np.array(residual, np.uint16, order="C")
+    M, N = x.shape
+    lib().xo_ve_fused_add_rms_norm(_p(x), _p(r), _p(np.ascontiguousarray(weight, np.uint16)), M, N,
+                                   C.c_float(eps))
+    return x, r
+
+
+def ve_act_and_mul(x, gelu=False):
+    x = np.ascontiguousarray(x, np.uint16)
+    M, N2 = x.shape
+    out = np.empty((M, N2 // 2), np.uint16)
+    lib().xo_ve_act_and_mul(_p(out), _p(x), N2 // 2, M, 1 if gelu else 0)
+    return out
+
+
+def ve_rotary_neox(data, cache, head_size, rot_dim=None):
+    d = np.array(data, np.uint16, order="C")
+    M = d.shape[0]
+    heads = d.size // (M * head_size)
+    rot_dim = head_size if rot_dim is None else rot_dim
+    lib().xo_ve_rotary_neox(_p(d), _p(np.ascontiguousarray(cache, np.float32)), head_size, heads, rot_dim, M)
+    return d
+
+
+def ve_dequant_act_mul(acc, scale_token, scale_channel, gelu=False):
+    acc = np.ascontiguousarray(acc, np.int32)
+    L, M, N = acc.shape if acc.ndim == 3 else (1,) + acc.shape
+    out = np.empty(acc.shape, np.uint16)
+    lib().xo_ve_dequant_act_mul(_p(out), _p(acc), _p(np.ascontiguousarray(scale_token, np.float32)),
+                                _p(np.ascontiguousarray(scale_channel, np.float32)), N // 2, M, L,
+                                1 if gelu else 0)
+    return out
+
+
+def ve_dequant_rotary(acc, scale_token, scale_channel, cos_sin):
+    acc = np.ascontiguousarray(acc, np.int32)
+    L, M, N = acc.shape if acc.ndim == 3 else (1,) + acc.shape
+    out = np.empty(acc.shape, np.uint16)
+    lib().xo_ve_dequant_rotary(_p(out), _p(acc), _p(np.ascontiguousarray(scale_token, np.float32)),
+                               _p(np.ascontiguousarray(scale_channel, np.float32)),
+                               _p(np.ascontiguousarray(cos_sin, np.float32)), M, N, L)
+    return out

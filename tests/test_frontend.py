@@ -116,6 +116,20 @@ def test_reference_generated_kernels_compile_unmodified(capi, tmp_path):
 
 
 @needs_reference
+def test_reference_generated_pipelines_compile_unmodified(capi, tmp_path):
+    """generate_pipeline.py (bf16 and W8A8, SwiGLU and GeGLU models) emits whole-layer benchmarks --
+    fused stages, the engine-style arm (vllm_ops.hpp) and the naive arm -- that build as they are."""
+    for preset, extra in [("llama3_8b", []), ("llama3_8b", ["--int8-mode", "w8a8"]), ("gemma2_9b", []),
+                          ("llama3_70b", ["--autotune"])]:
+        name = preset + "".join(extra).replace("-", "_")
+        src = tmp_path / f"{name}.cpp"
+        subprocess.check_call([sys.executable, "generate_pipeline.py", "--preset", preset, "--output", str(src)]
+                              + extra, cwd=os.path.join(REF, "autotune"), stdout=subprocess.DEVNULL,
+                              stderr=subprocess.DEVNULL)
+        compile_cpp(str(src), str(tmp_path / name))
+
+
+@needs_reference
 def test_reference_test_mains_compile_unmodified(capi, tmp_path):
     """tests/test_k*.cpp and the MoE examples of the reference build against the front end as they are."""
     for t in ["tests/test_k1.cpp", "tests/test_k2.cpp", "tests/test_k3.cpp", "tests/test_k4.cpp",

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libxefuse_b200.so")
-SOURCES = ["xf_gemm.cu", "xf_standalone.cu", "xf_harness.cu"]
+SOURCES = ["xf_gemm.cu", "xf_standalone.cu", "xf_rowops.cu", "xf_harness.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -70,6 +70,8 @@ EXPORTS = [
     "xf_sa_scale_rows", "xf_sa_scale_cols", "xf_sa_add_residual", "xf_sa_residual_gamma",
     "xf_sa_swiglu", "xf_sa_geglu", "xf_sa_rope", "xf_sa_rope_scaled", "xf_sa_unary",
     "xf_sa_bias_add", "xf_sa_dequant_w8a8", "xf_compute_rstd", "xf_compute_rstd_and_quantize",
+    "xf_ve_rms_norm", "xf_ve_fused_add_rms_norm", "xf_ve_act_and_mul", "xf_ve_rotary_embedding",
+    "xf_ve_dequant_act_mul", "xf_ve_dequant_rotary",
     "xf_harness_fill_uniform", "xf_harness_ref_gemm", "xf_harness_compare",
 ]
 
@@ -111,6 +113,12 @@ def lib():
     L.xf_sa_dequant_w8a8.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp]
     L.xf_compute_rstd.argtypes = [vp, vp, i32, i32, i32, f32, vp]
     L.xf_compute_rstd_and_quantize.argtypes = [vp, vp, vp, i32, i32, i32, f32, vp]
+    L.xf_ve_rms_norm.argtypes = [vp, vp, vp, i32, i32, f32, vp]
+    L.xf_ve_fused_add_rms_norm.argtypes = [vp, vp, vp, i32, i32, f32, vp]
+    L.xf_ve_act_and_mul.argtypes = [vp, vp, i32, i32, i32, vp]
+    L.xf_ve_rotary_embedding.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    L.xf_ve_dequant_act_mul.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    L.xf_ve_dequant_rotary.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp]
     _lib = L
     return L
 
@@ -304,3 +312,41 @@ def _lmn(t):
     if t.dim() == 3:
         return t.shape[0], t.shape[1], t.shape[2]
     return 1, t.shape[0], t.shape[1]
+
+
+# ---- engine-style row passes (xf_ve_*): the comparison arm of the reference's pipelines ----------
+def ve_rms_norm(out, inp, weight, eps=1e-6):
+    M, N = inp.shape
+    check(lib().xf_ve_rms_norm(out.data_ptr(), inp.data_ptr(), weight.data_ptr(), M, N, eps, _stream()))
+
+
+def ve_fused_add_rms_norm(inp, residual, weight, eps=1e-6):
+    M, N = inp.shape
+    check(lib().xf_ve_fused_add_rms_norm(inp.data_ptr(), residual.data_ptr(), weight.data_ptr(), M, N, eps,
+                                         _stream()))
+
+
+def ve_act_and_mul(out, inp, gelu=False):
+    M, d = out.shape
+    check(lib().xf_ve_act_and_mul(out.data_ptr(), inp.data_ptr(), d, M, 1 if gelu else 0, _stream()))
+
+
+def ve_rotary_embedding(query, key, cos_sin_cache, head_size, rot_dim=None):
+    M = query.shape[0]
+    rot_dim = head_size if rot_dim is None else rot_dim
+    nq = query.numel() // (M * head_size)
+    nk = key.numel() // (M * head_size) if key is not None else 0
+    check(lib().xf_ve_rotary_embedding(query.data_ptr(), key.data_ptr() if key is not None else None,
+                                       cos_sin_cache.data_ptr(), head_size, nq, nk, rot_dim, M, _stream()))
+
+
+def ve_dequant_act_mul(out, acc, scale_token, scale_channel, gelu=False):
+    L_, M, N = _lmn(out)
+    check(lib().xf_ve_dequant_act_mul(out.data_ptr(), acc.data_ptr(), scale_token.data_ptr(),
+                                      scale_channel.data_ptr(), N // 2, M, L_, 1 if gelu else 0, _stream()))
+
+
+def ve_dequant_rotary(out, acc, scale_token, scale_channel, cos_sin):
+    L_, M, N = _lmn(out)
+    check(lib().xf_ve_dequant_rotary(out.data_ptr(), acc.data_ptr(), scale_token.data_ptr(),
+                                     scale_channel.data_ptr(), cos_sin.data_ptr(), M, N, L_, _stream()))

@@ -301,18 +301,18 @@ __global__ void __launch_bounds__(256) rstd_kernel(const __nv_bfloat16* __restri
 // RMS-normalise + absmax-quantise with ONE pass over HBM: the row is staged in shared memory as it
 // is read (16-byte loads), the two reductions and the quantisation then run from shared memory and
 // the int8 row is written with 16-byte stores.  Needs N % 16 == 0 and a row that fits shared memory.
-__global__ void __launch_bounds__(256) rstd_quant_smem_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(1024) rstd_quant_smem_kernel(const __nv_bfloat16* __restrict__ x,
                                                               float* __restrict__ scale_out,
                                                               int8_t* __restrict__ xq, long long rows,
                                                               int N, float eps) {
   extern __shared__ __align__(16) unsigned char row_smem[];
-  __shared__ float red[8];
+  __shared__ float red[32];
   uint4* srow = reinterpret_cast<uint4*>(row_smem);
   const int nvec = N / 8;  // 8 bf16 per 16-byte vector
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * N);
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < nvec; i += 256) {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
       const uint4 u = xr[i];
       srow[i] = u;
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(256) rstd_quant_smem_kernel(const __nv_bfloat1
     ss = block_reduce<false>(ss, red);   // also orders the shared-memory writes before the reads below
     const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
     float mx = 0.0f;
-    for (int i = threadIdx.x; i < nvec; i += 256) {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
       const uint4 u = srow[i];
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(256) rstd_quant_smem_kernel(const __nv_bfloat1
     mx = block_reduce<true>(mx, red);
     const float scale = mx / 127.0f + 1e-8f;
     uint4* qr = reinterpret_cast<uint4*>(xq + row * N);
-    for (int i = threadIdx.x; i < nvec / 2; i += 256) {   // 16 int8 per 16-byte store
+    for (int i = threadIdx.x; i < nvec / 2; i += blockDim.x) {   // 16 int8 per 16-byte store
       uint32_t o[4];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -361,6 +361,88 @@ __global__ void __launch_bounds__(256) rstd_quant_smem_kernel(const __nv_bfloat1
     }
     if (threadIdx.x == 0) scale_out[row] = scale;
     __syncthreads();  // the next row overwrites the staged one
+  }
+}
+
+// The same with the row held in registers instead of shared memory: each thread keeps VPT 16-byte
+// vectors (8 bf16 each) of the row, the sum of squares and the absolute maximum are reduced
+// together (max|x * rstd| == max|x| * rstd: rounding is monotone and rstd > 0), and the int8 row is
+// written from the registers.  One HBM read, one write, two block-wide reductions per row; the
+// next row a block will take is loaded before the current one is processed.  Rounding half away
+// from zero uses full-rate instructions only: q + 1.5 * 2^23 leaves round-to-nearest-even(q) in the
+// low mantissa bits, and an exact tie (q = k + 0.5, rare) is redone on q +- 0.5, an integer.
+template <int VPT>
+__global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             float* __restrict__ scale_out,
+                                                             int8_t* __restrict__ xq, long long rows,
+                                                             int N, float eps) {
+  __shared__ float red[32];
+  const int nvec = N / 8;
+  auto load_row = [&](uint4 (&dst)[VPT], long long row) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * N);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      dst[k] = (i < nvec) ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  uint4 v[VPT], vn[VPT];
+  if (blockIdx.x < rows) load_row(v, blockIdx.x);
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    // the next row's loads are in flight while this one is reduced and quantised
+    const long long next = row + gridDim.x;
+    if (next < rows) load_row(vn, next);
+    float ss = 0.0f, amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float a = __uint_as_float(w[t] << 16), b = __uint_as_float(w[t] & 0xFFFF0000u);
+        ss += a * a + b * b;
+        amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+      }
+    }
+    ss = block_reduce<false>(ss, red);
+    amax = block_reduce<true>(amax, red);
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
+    const float scale = (amax * rstd) / 127.0f + 1e-8f;
+    const float inv_scale = 1.0f / scale;   // one division per row; the elements multiply
+    uint2* qr = reinterpret_cast<uint2*>(xq + row * N);   // 8 int8 per vector
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nvec) {
+        const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+        // |x * rstd| <= amax * rstd < 127 * scale, so q stays inside [-127.5, 127.5]: no clamp needed
+        const float kMagic = 12582912.0f;   // 1.5 * 2^23: q + kMagic holds rne(q) in its low bits
+        float q[8], m[8];
+        bool tie = false;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          q[2 * t] = (__uint_as_float(w[t] << 16) * rstd) * inv_scale;
+          q[2 * t + 1] = (__uint_as_float(w[t] & 0xFFFF0000u) * rstd) * inv_scale;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          m[e] = q[e] + kMagic;
+          tie |= fabsf(q[e] - (m[e] - kMagic)) == 0.5f;
+        }
+        if (tie) {   // an exact k + 0.5 somewhere in these 8: round those away from zero
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (fabsf(q[e] - (m[e] - kMagic)) == 0.5f) m[e] = (q[e] + copysignf(0.5f, q[e])) + kMagic;
+        }
+        uint32_t o[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          o[e >> 2] |= (static_cast<uint32_t>(__float_as_int(m[e]) - 0x4B400000) & 0xFFu) << (8 * (e & 3));
+        qr[i] = make_uint2(o[0], o[1]);
+      }
+    }
+    if (threadIdx.x == 0) scale_out[row] = scale;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) v[k] = vn[k];
   }
 }
 
@@ -480,11 +562,31 @@ static xf_status launch_rstd(const void* x, float* out, int8_t* xq, int M, int N
   const size_t row_bytes = static_cast<size_t>(N) * 2;
   const bool one_pass = xq && (N % 16 == 0) && row_bytes <= 96 * 1024 &&
                         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15) == 0;
-  if (one_pass) {
+  const int nvec = N / 8;
+  const bool in_regs = xq && (N % 8 == 0) && nvec <= 4096 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(xq) & 7) == 0;
+  if (in_regs) {
+    // the fewest vectors per thread that keep the block at 256 threads or fewer (many rows in
+    // flight per SM); rows beyond 8 x 256 vectors take 8 per thread and up to 512 threads
+    const auto* xb = static_cast<const __nv_bfloat16*>(x);
+    const int g = static_cast<int>(grid);
+    int vpt = 1;
+    while (vpt < 8 && (nvec + vpt - 1) / vpt > 256) vpt *= 2;
+    int threads = (((nvec + vpt - 1) / vpt + 31) / 32) * 32;
+    if (threads < 64) threads = 64;
+    switch (vpt) {
+      case 1: xf::sa::rstd_quant_reg_kernel<1><<<g, threads, 0, st>>>(xb, out, xq, rows, N, eps); break;
+      case 2: xf::sa::rstd_quant_reg_kernel<2><<<g, threads, 0, st>>>(xb, out, xq, rows, N, eps); break;
+      case 4: xf::sa::rstd_quant_reg_kernel<4><<<g, threads, 0, st>>>(xb, out, xq, rows, N, eps); break;
+      default: xf::sa::rstd_quant_reg_kernel<8><<<g, threads, 0, st>>>(xb, out, xq, rows, N, eps); break;
+    }
+  } else if (one_pass) {
     if (row_bytes > 48 * 1024)
       cudaFuncSetAttribute(xf::sa::rstd_quant_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(row_bytes));
-    xf::sa::rstd_quant_smem_kernel<<<static_cast<int>(grid), 256, row_bytes, st>>>(
+    // enough threads per block that a few staged rows fill the SM's thread slots
+    const int threads = row_bytes > 32 * 1024 ? 1024 : (row_bytes > 16 * 1024 ? 512 : 256);
+    xf::sa::rstd_quant_smem_kernel<<<static_cast<int>(grid), threads, row_bytes, st>>>(
         static_cast<const __nv_bfloat16*>(x), out, xq, rows, N, eps);
   } else if (xq)
     xf::sa::rstd_kernel<true><<<static_cast<int>(grid), 256, 0, st>>>(
