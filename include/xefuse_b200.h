@@ -136,6 +136,14 @@ typedef struct xf_epilogue_desc {
                              cos_sin[m, n % P] (one head_dim-wide table shared by all heads);
                              P must be a multiple of 32 */
   int32_t out_layout;     /* xf_out_layout */
+  /* Optional side output for a following RMSNorm: per row, the sums of squares of the final fp32
+   * values v (before the rounding to bf16) over each group of 32 consecutive columns, laid out
+   * [L][ceil(N/32)][M] floats (xf_row_sumsq_count gives the element count).  Every slot is written
+   * exactly once per launch, without atomics: no zeroing needed, results are deterministic.
+   * xf_reduce_partials_rsqrt turns them into rstd[m].  Needs pair == none and the full layout.
+   * The reference's counterpart is the per-tile ColReduction of K0a_CR
+   * (kernels/gemm_residual_gamma_colred.hpp:89-115). */
+  float* row_sumsq;
 } xf_epilogue_desc;
 
 typedef struct xf_gemm_desc {
@@ -259,6 +267,13 @@ XF_API xf_status xf_compute_rstd(const void* x, float* rstd, int M, int N, int L
  * rstd (compute_rstd.hpp:67-125). */
 XF_API xf_status xf_compute_rstd_and_quantize(const void* x, int8_t* xq, float* scale_token,
                                               int M, int N, int L, float eps, void* stream);
+
+/* Number of floats xf_epilogue_desc.row_sumsq must hold for an M x N x L problem. */
+XF_API size_t xf_row_sumsq_count(int M, int N, int L);
+/* rstd[l*M+m] = 1/sqrt(sum of row m's partials / N + eps) from the row_sumsq side output of a fused
+ * GEMM (launch_reduce_partials_rsqrt, kernels/gemm_residual_gamma_colred.hpp:199-226). */
+XF_API xf_status xf_reduce_partials_rsqrt(const float* partials, float* rstd, int M, int N, int L,
+                                          float eps, void* stream);
 
 /*
  * Engine-style stand-alone passes: the comparison arm of the reference's generated pipelines

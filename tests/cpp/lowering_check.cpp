@@ -10,6 +10,7 @@
 #include "xe-fuse/kernels/gemm_dequant_w8a8.hpp"
 #include "xe-fuse/kernels/gemm_dual_output.hpp"
 #include "xe-fuse/kernels/gemm_residual_gamma.hpp"
+#include "xe-fuse/kernels/gemm_residual_gamma_colred.hpp"
 #include "xe-fuse/kernels/gemm_rmsnorm.hpp"
 #include "xe-fuse/kernels/gemm_rmsnorm_rope.hpp"
 #include "xe-fuse/kernels/gemm_rmsnorm_swiglu.hpp"
@@ -30,7 +31,7 @@ static bf16* const kRes = reinterpret_cast<bf16*>(0x5000);
 static bf16* const kAux = reinterpret_cast<bf16*>(0x6000);
 
 template <class Kt, class EvtArgs>
-static void show(const char* name, EvtArgs const& ea, xefuse::Extensions ext = {}) {
+static void show(const char* name, EvtArgs const& ea, xefuse::Extensions ext = {}, const void* ptr_c = nullptr) {
   using Op = typename Kt::Gemm;
   using Kernel = typename Op::GemmKernel;
   auto sA = cutlass::make_cute_packed_stride(typename Kernel::StrideA{}, make_shape(M, K, L));
@@ -39,18 +40,19 @@ static void show(const char* name, EvtArgs const& ea, xefuse::Extensions ext = {
   typename Kernel::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, L},
                                   {reinterpret_cast<typename Kernel::ElementA*>(0x10000), sA,
                                    reinterpret_cast<typename Kernel::ElementB*>(0x20000), sB},
-                                  {ea, nullptr, sD, reinterpret_cast<typename Kernel::ElementD*>(0x30000), sD}, {}};
+                                  {ea, static_cast<typename Kernel::ElementC const*>(ptr_c), sD,
+                                   reinterpret_cast<typename Kernel::ElementD*>(0x30000), sD}, {}};
   xf_gemm_desc d;
   cutlass::Status ls = Op::lower(args, ext, d);
   cutlass::Status cs = Op::can_implement(args, ext);
   auto at = [](const void* p) { return (unsigned)(reinterpret_cast<uintptr_t>(p)); };
   std::printf("%s lower=%d can=%d ab=%d d=%d lda=%lld ldb=%lld ldd=%lld tile=%d,%d,%d res=%d@%x aux=%d@%x "
-              "row=%d@%x/%g col=%d@%x bias=%d@%x unary=%d pair=%d cs=%x period=%d layout=%d\n",
+              "row=%d@%x/%g col=%d@%x bias=%d@%x unary=%d pair=%d cs=%x period=%d layout=%d sumsq=%x\n",
               name, int(ls), int(cs), d.dtype_ab, d.dtype_d, (long long)d.lda, (long long)d.ldb, (long long)d.ldd,
               d.tile_m, d.tile_n, d.tile_k, d.epi.residual.enabled, at(d.epi.residual.ptr), d.epi.aux_store.enabled,
               at(d.epi.aux_store.ptr), d.epi.row_scale.enabled, at(d.epi.row_scale.ptr), d.epi.row_scale.null_default,
               d.epi.col_scale.enabled, at(d.epi.col_scale.ptr), d.epi.bias.enabled, at(d.epi.bias.ptr), d.epi.unary,
-              d.epi.pair, at(d.epi.cos_sin.ptr), d.epi.cos_sin_period, d.epi.out_layout);
+              d.epi.pair, at(d.epi.cos_sin.ptr), d.epi.cos_sin_period, d.epi.out_layout, at(d.epi.row_sumsq));
 }
 
 template <class EVT, class EA = bf16, class EAcc = float>
@@ -86,6 +88,15 @@ int main() {
     show<Mk<EVT>>("k4v2_table", ea, e);
   }
   show<xe_fuse::GemmResidualGamma<>>("k0a", xe_fuse::GemmResidualGamma<>::make_evt_args(kRes, sMN, kCol, N));
+  {
+    // K0a with the sum of squares folded in: the residual is the kernel's source tensor C
+    using CR = xe_fuse::GemmResidualGammaColRed<>;
+    float* const kSumSq = reinterpret_cast<float*>(0x7000);
+    show<CR>("k0a_cr", CR::make_evt_args(kCol, N, kSumSq, M), {}, kRes);
+    show<CR>("k0a_cr_null", CR::make_evt_args(kCol, N, nullptr, M), {}, kRes);    // reduction disabled
+    show<CR>("bad_cr_no_source", CR::make_evt_args(kCol, N, kSumSq, M));           // SrcFetch without C
+    show<xe_fuse::GemmRmsNorm<>>("bad_unused_source", xe_fuse::GemmRmsNorm<>::make_evt_args(kRow, M), {}, kRes);
+  }
   show<xe_fuse::GemmDualOutput<>>("k0_dual", xe_fuse::GemmDualOutput<>::make_evt_args(kRes, sMN, kCol, N, kAux, sMN));
   show<xe_fuse::GemmDequantW8A8<>>("w8a8", xe_fuse::GemmDequantW8A8<>::make_evt_args(kRow, M, kCol, N));
   {

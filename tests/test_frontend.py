@@ -75,6 +75,8 @@ def test_lowering_of_every_preset_tree(capi):
     assert r["k3"]["pair"] == "3" and r["k3"]["cs"] == "4000" and r["k3"]["row"].startswith("0@")
     assert r["k4"]["pair"] == "3" and r["k4"]["row"] == "1@1000/1" and r["k4v2_table"]["period"] == "128"
     assert r["k0a"]["res"] == "1@5000" and r["k0a"]["col"] == "1@2000" and r["k0a"]["aux"] == "0@0"
+    assert ok("k0a_cr") and r["k0a_cr"]["res"] == "1@5000" and r["k0a_cr"]["col"] == "1@2000"
+    assert r["k0a_cr"]["sumsq"] == "7000" and ok("k0a_cr_null") and r["k0a_cr_null"]["sumsq"] == "0"
     assert r["k0_dual"]["aux"] == "1@6000" and r["k0_dual"]["res"] == "1@5000" and r["k0_dual"]["col"] == "1@2000"
     assert r["w8a8"]["ab"] == "1" and r["w8a8"]["row"] == "1@1000/1" and r["w8a8"]["col"] == "1@2000"
     assert r["w8a8_biased"]["bias"] == "1@3000"
@@ -85,7 +87,8 @@ def test_lowering_of_every_preset_tree(capi):
     assert r["bare"]["row"].startswith("0@") and r["bare_alpha2"]["row"] == "1@0/2"
     # B is [K,N] row-major: ldb is the N extent although make_shape is called with (N,K,L)
     assert r["k1"]["lda"] == "128" and r["k1"]["ldb"] == "512" and r["k1"]["ldd"] == "512"
-    for n in ["bad_beta", "bad_scale_after_unary", "bad_residual_after_scale", "bad_hadamard", "bad_acc_twice"]:
+    for n in ["bad_beta", "bad_scale_after_unary", "bad_residual_after_scale", "bad_hadamard", "bad_acc_twice",
+              "bad_cr_no_source", "bad_unused_source"]:
         assert rows[n]["lower"] == "5" and rows[n]["can"] == "5", (n, rows[n])   # kErrorNotSupported
 
 
@@ -133,7 +136,8 @@ def test_reference_generated_pipelines_compile_unmodified(capi, tmp_path):
 def test_reference_test_mains_compile_unmodified(capi, tmp_path):
     """tests/test_k*.cpp and the MoE examples of the reference build against the front end as they are."""
     for t in ["tests/test_k1.cpp", "tests/test_k2.cpp", "tests/test_k3.cpp", "tests/test_k4.cpp",
-              "tests/test_k0a.cpp", "tests/test_k8.cpp", "tests/test_k2_w8a8.cpp", "tests/test_k4_w8a8.cpp",
+              "tests/test_k0a.cpp", "tests/test_k0a_colred.cpp", "tests/test_k8.cpp", "tests/test_k2_w8a8.cpp",
+              "tests/test_k4_w8a8.cpp",
               "examples/moe_expert_builder.cpp", "examples/moe_expert_fused.cpp"]:
         compile_cpp(os.path.join(REF, t), str(tmp_path / os.path.basename(t)[:-4]))
 

@@ -46,7 +46,8 @@ class XfMat(C.Structure):
 class XfEpilogueDesc(C.Structure):
     _fields_ = [("residual", XfMat), ("aux_store", XfMat), ("row_scale", XfVec),
                 ("col_scale", XfVec), ("bias", XfVec), ("unary", C.c_int32), ("pair", C.c_int32),
-                ("cos_sin", XfMat), ("cos_sin_period", C.c_int32), ("out_layout", C.c_int32)]
+                ("cos_sin", XfMat), ("cos_sin_period", C.c_int32), ("out_layout", C.c_int32),
+                ("row_sumsq", C.c_void_p)]
 
 
 class XfGemmDesc(C.Structure):
@@ -70,6 +71,7 @@ EXPORTS = [
     "xf_sa_scale_rows", "xf_sa_scale_cols", "xf_sa_add_residual", "xf_sa_residual_gamma",
     "xf_sa_swiglu", "xf_sa_geglu", "xf_sa_rope", "xf_sa_rope_scaled", "xf_sa_unary",
     "xf_sa_bias_add", "xf_sa_dequant_w8a8", "xf_compute_rstd", "xf_compute_rstd_and_quantize",
+    "xf_row_sumsq_count", "xf_reduce_partials_rsqrt",
     "xf_ve_rms_norm", "xf_ve_fused_add_rms_norm", "xf_ve_act_and_mul", "xf_ve_rotary_embedding",
     "xf_ve_dequant_act_mul", "xf_ve_dequant_rotary",
     "xf_harness_fill_uniform", "xf_harness_ref_gemm", "xf_harness_compare",
@@ -113,6 +115,9 @@ def lib():
     L.xf_sa_dequant_w8a8.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp]
     L.xf_compute_rstd.argtypes = [vp, vp, i32, i32, i32, f32, vp]
     L.xf_compute_rstd_and_quantize.argtypes = [vp, vp, vp, i32, i32, i32, f32, vp]
+    L.xf_row_sumsq_count.argtypes = [i32, i32, i32]
+    L.xf_row_sumsq_count.restype = C.c_size_t
+    L.xf_reduce_partials_rsqrt.argtypes = [vp, vp, i32, i32, i32, f32, vp]
     L.xf_ve_rms_norm.argtypes = [vp, vp, vp, i32, i32, f32, vp]
     L.xf_ve_fused_add_rms_norm.argtypes = [vp, vp, vp, i32, i32, f32, vp]
     L.xf_ve_act_and_mul.argtypes = [vp, vp, i32, i32, i32, vp]
@@ -164,10 +169,11 @@ class GemmPlan:
 
     def __init__(self, A, B, D, *, residual=None, aux_store=None, row_scale=None, col_scale=None,
                  bias=None, unary="none", pair="none", cos_sin=None, cos_sin_period=0,
-                 compact=False, flags=0, tile=(256, 256, 32), a_k_slabs=False, d_peer_ptrs=()):
+                 compact=False, flags=0, tile=(256, 256, 32), a_k_slabs=False, d_peer_ptrs=(),
+                 row_sumsq=None):
         import torch
         L_ = lib()
-        self._keep = [A, B, D, residual, aux_store, row_scale, col_scale, bias, cos_sin]
+        self._keep = [A, B, D, residual, aux_store, row_scale, col_scale, bias, cos_sin, row_sumsq]
         batched = A.dim() == 3 and not a_k_slabs
         Lb = A.shape[0] if batched else 1
         M, K = A.shape[-2], A.shape[-1]
@@ -200,6 +206,7 @@ class GemmPlan:
         e.cos_sin = mat(cos_sin)
         e.cos_sin_period = cos_sin_period
         e.out_layout = OUT_COMPACT if compact else OUT_FULL
+        e.row_sumsq = row_sumsq.data_ptr() if row_sumsq is not None else None
         self.desc = d
         check(L_.xf_gemm_can_implement(C.byref(d)))
         ws = C.c_size_t(0)
@@ -350,3 +357,8 @@ def ve_dequant_rotary(out, acc, scale_token, scale_channel, cos_sin):
     L_, M, N = _lmn(out)
     check(lib().xf_ve_dequant_rotary(out.data_ptr(), acc.data_ptr(), scale_token.data_ptr(),
                                      scale_channel.data_ptr(), cos_sin.data_ptr(), M, N, L_, _stream()))
+
+
+def reduce_partials_rsqrt(partials, rstd, M, N, L=1, eps=1e-6):
+    """rstd from the row_sumsq side output of a fused GEMM."""
+    check(lib().xf_reduce_partials_rsqrt(partials.data_ptr(), rstd.data_ptr(), M, N, L, eps, _stream()))

@@ -239,6 +239,16 @@ static xf_status validate(const xf_gemm_desc* d) {
     set_error("ldd=%lld smaller than the %d output columns", (long long)d->ldd, n_out);
     return XF_ERR_INVALID_LAYOUT;
   }
+  if (e.row_sumsq) {
+    if (e.pair != XF_PAIR_NONE || compact) {
+      set_error("row_sumsq needs an epilogue without a pair op and the full output layout");
+      return XF_ERR_NOT_SUPPORTED;
+    }
+    if (d->dtype_d == XF_DT_S32) {
+      set_error("row_sumsq needs a floating-point epilogue (dtype_d bf16 or f32)");
+      return XF_ERR_NOT_SUPPORTED;
+    }
+  }
   xf_status s;
   if ((s = check_vec(e.row_scale, "row_scale")) != XF_SUCCESS) return s;
   if ((s = check_vec(e.col_scale, "col_scale")) != XF_SUCCESS) return s;
@@ -474,6 +484,7 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   p.epi.unary = e.unary;
   p.epi.pair = e.pair;
   p.epi.compact = (e.out_layout == XF_OUT_COMPACT) ? 1 : 0;
+  p.epi.row_sumsq = e.row_sumsq;
 
   const int n_out = p.epi.compact ? d->N / 2 : d->N;
   const bool tma_store_ok = d->dtype_d == XF_DT_BF16 && aligned16(d->D) && (d->ldd * 2) % 16 == 0 &&

@@ -679,6 +679,17 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             continue;
           }
           epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs);
+          if (e.row_sumsq != nullptr) {
+            // side output for a following RMSNorm: this row's sum of squares over these 32 columns
+            const int nv = p.N - (n0 + tcol0);
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ss += (i < nv) ? v[i] * v[i] : 0.0f;
+            if (row_ok) {
+              const long long units = (p.N + 31) >> 5;
+              e.row_sumsq[(static_cast<long long>(l) * units + ((n0 + tcol0) >> 5)) * p.M + row] = ss;
+            }
+          }
           if (p.d_dtype == DT_F32) {
             if (row_ok) {
               float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(l) * p.batch_d +

@@ -48,6 +48,7 @@ struct EpiParams {
   int unary;
   int pair;
   int compact;  // 1: D holds one value per column pair, [M, N/2]
+  float* row_sumsq;   // optional [L][ceil(N/32)][M] sums of squares of the final values, or null
 };
 
 struct alignas(64) GemmParams {

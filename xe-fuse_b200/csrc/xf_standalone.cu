@@ -446,6 +446,21 @@ __global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16
   }
 }
 
+// rstd[l*M+m] = 1/sqrt(sum_u partials[l][u][m] / N + eps): the finishing pass over the row_sumsq
+// side output of a fused GEMM.  One thread per row; consecutive threads read consecutive floats.
+__global__ void __launch_bounds__(256) reduce_partials_rsqrt_kernel(const float* __restrict__ partials,
+                                                                    float* __restrict__ rstd, int M, int units,
+                                                                    long long rows, float inv_n, float eps) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  const long long l = i / M;
+  const int m = static_cast<int>(i - l * M);
+  const float* p = partials + l * units * static_cast<long long>(M) + m;
+  float ss = 0.0f;
+  for (int u = 0; u < units; ++u) ss += p[static_cast<long long>(u) * M];
+  rstd[i] = 1.0f / sqrtf(ss * inv_n + eps);
+}
+
 }  // namespace sa
 }  // namespace xf
 
@@ -613,6 +628,29 @@ xf_status xf_compute_rstd_and_quantize(const void* x, int8_t* xq, float* scale_t
     return XF_ERR_INVALID_PROBLEM;
   }
   return launch_rstd(x, scale_token, xq, M, N, L, eps, stream);
+}
+
+size_t xf_row_sumsq_count(int M, int N, int L) {
+  if (M <= 0 || N <= 0 || L <= 0) return 0;
+  return static_cast<size_t>(L) * static_cast<size_t>((N + 31) / 32) * static_cast<size_t>(M);
+}
+
+xf_status xf_reduce_partials_rsqrt(const float* partials, float* rstd, int M, int N, int L, float eps,
+                                   void* stream) {
+  if (!partials || !rstd || M <= 0 || N <= 0 || L <= 0) {
+    xf::set_error("reduce_partials_rsqrt: bad arguments");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  const long long rows = static_cast<long long>(M) * L;
+  const int grid = static_cast<int>((rows + 255) / 256);
+  xf::sa::reduce_partials_rsqrt_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      partials, rstd, M, (N + 31) / 32, rows, 1.0f / static_cast<float>(N), eps);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    xf::set_error("reduce_partials_rsqrt launch failed: %s", cudaGetErrorString(e));
+    return XF_ERR_INTERNAL;
+  }
+  return XF_SUCCESS;
 }
 
 }  // extern "C"

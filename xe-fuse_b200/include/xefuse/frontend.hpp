@@ -96,6 +96,10 @@ template <class T> struct multiplies { T operator()(T a, T b) const { return a *
 template <class T> struct plus { T operator()(T a, T b) const { return a + b; } };
 template <class T> struct minus { T operator()(T a, T b) const { return a - b; } };
 
+namespace epilogue::thread {
+template <class T> struct Identity { T operator()(T a) const { return a; } };
+}  // namespace epilogue::thread
+
 struct MatrixCoord {
   int r = 0, c = 0;
   MatrixCoord() = default;
@@ -187,7 +191,7 @@ enum Stage : int { kAcc = 0, kResidual, kAuxStore, kRow, kCol, kBias, kUnary, kP
 
 // What a subtree evaluates to while lowering.
 struct Val {
-  enum Kind { kInvalid, kValue, kRowVec, kColVec, kMat } kind = kInvalid;
+  enum Kind { kInvalid, kValue, kRowVec, kColVec, kMat, kSquare } kind = kInvalid;
   int stage = kAcc;           // kValue: last step of the flat program this value has been through
   const void* ptr = nullptr;  // leaves
   int dtype = XF_DT_F32;
@@ -202,6 +206,10 @@ struct Ctx {
   int acc_uses = 0;
   bool acc_bound = false;     // inside a split tree's output tree, Acc names the input tree's value
   Val acc_binding;
+  int sumsq_stage = -1;       // flat-program step of the value a column reduction squares
+  bool has_src = false;       // the caller passed a source tensor C (ptr_C); a SrcFetch leaf reads it
+  bool src_used = false;
+  Val src;
   Ctx() { std::memset(&epi, 0, sizeof(epi)); }
   Val fail(const char* msg) {
     if (ok) why = msg;
@@ -226,6 +234,12 @@ inline xf_mat to_mat(Val const& v) {
 }
 
 inline Val lower_mul(Val a, Val b, Ctx& c) {
+  if (a.kind == Val::kValue && b.kind == Val::kValue && c.acc_bound && a.stage == b.stage) {
+    // Acc * Acc inside an auxiliary tree of a split: the square of the input tree's value, which
+    // only a column reduction may consume
+    a.kind = Val::kSquare;
+    return a;
+  }
   if (a.kind != Val::kValue) std::swap(a, b);
   if (a.kind != Val::kValue) return c.fail("a product needs the running value as one operand");
   if (b.kind == Val::kRowVec) {
@@ -377,6 +391,27 @@ struct Sm90SplitTreeVisitor {
                                typename OutputTree::Arguments>;
 };
 
+// The source tensor C of the kernel (EpilogueArguments::ptr_C / dC) as a leaf.
+template <class Element>
+struct Sm90SrcFetch { struct Arguments {}; };
+template <class Element> using XeSrcFetch = Sm90SrcFetch<Element>;
+
+// Reduction of a value along N into one number per row ("column reduction": the result is a column
+// vector).  Supported form: the sum of Acc * Acc inside an auxiliary tree of a split, written as
+// partial sums that launch_reduce_partials_rsqrt finishes; ptr_col is the partials buffer.
+template <template <class> class RegReduceFn, template <class> class ShuffleReduceFn,
+          template <class> class GmemReduceFn, int Stages, class TileShape, class Element,
+          class ElementCompute = float, FloatRoundStyle Round = FloatRoundStyle::round_to_nearest,
+          class StrideMNL = cute::Stride<cute::_1, cute::_0, int64_t>, int Alignment = 4,
+          bool EnableNullptr = true, bool FinalReduction = true>
+struct XeColReduction {
+  struct Arguments {
+    Element* ptr_col = nullptr;
+    ElementCompute reduction_identity = ElementCompute(0);
+    StrideMNL dCol = {};
+  };
+};
+
 // Default fusion when a CollectiveBuilder is given no EVT: D = alpha * acc + beta * C.
 template <class ElementOutput, class ElementCompute = float>
 struct LinearCombination {
@@ -478,6 +513,44 @@ struct Lower<fus::XeEVT<fus::XeAuxStore<E, St, Cp, Al, En, B2>, X>> {
   }
 };
 
+template <class E>
+struct Lower<fus::Sm90SrcFetch<E>> {
+  template <class Args>
+  static Val apply(Args const&, Ctx& c) {
+    if (!c.has_src) return c.fail("SrcFetch without a source tensor (ptr_C is null)");
+    if (DType<E>::value != c.src.dtype) return c.fail("SrcFetch element type differs from ElementC");
+    c.src_used = true;
+    return c.src;
+  }
+};
+
+// Identity on a value: EVT<Compute<Identity>, X>
+template <class EO, class EC, cutlass::FloatRoundStyle R, class X>
+struct Lower<fus::XeEVT<fus::XeCompute<cutlass::epilogue::thread::Identity, EO, EC, R>, X>> {
+  template <class Args>
+  static Val apply(Args const& t, Ctx& c) { return lower<X>(std::get<0>(t), c); }
+};
+
+// Sum over N of a squared value: EVT<ColReduction<plus...>, Mul<Acc, Acc>> in an auxiliary tree
+template <int S, class TS, class E, class EC, cutlass::FloatRoundStyle R, class St, int Al, bool En, bool Fin,
+          class X>
+struct Lower<fus::XeEVT<fus::XeColReduction<cutlass::plus, cutlass::plus, cutlass::plus, S, TS, E, EC, R, St, Al,
+                                            En, Fin>, X>> {
+  template <class Args>
+  static Val apply(Args const& t, Ctx& c) {
+    Val v = lower<X>(std::get<0>(t), c);
+    if (!c.ok) return Val{};
+    if (v.kind != Val::kSquare) return c.fail("a column reduction is supported on Acc * Acc only");
+    if (!std::is_same<E, float>::value) return c.fail("the partial sums of squares are fp32");
+    auto const& r = std::get<1>(t);
+    if (float(r.reduction_identity) != 0.f) return c.fail("a sum needs the reduction identity 0");
+    c.epi.row_sumsq = reinterpret_cast<float*>(r.ptr_col);   // null pointer: reduction disabled
+    c.sumsq_stage = v.stage;
+    v.kind = Val::kValue;   // auxiliary trees hand the input tree's value on unchanged
+    return v;
+  }
+};
+
 template <class In, class Out, class... Aux>
 struct Lower<fus::Sm90SplitTreeVisitor<In, Out, Aux...>> {
   template <class Args, std::size_t... I>
@@ -495,6 +568,9 @@ struct Lower<fus::Sm90SplitTreeVisitor<In, Out, Aux...>> {
     if (!c.ok) return Val{};
     Val out = lower<Out>(std::get<sizeof...(Aux) + 1>(t), c);
     c.acc_bound = false;
+    // the kernel squares the final value: the reduced value must be what the output tree stores
+    if (c.ok && c.epi.row_sumsq != nullptr && (out.kind != Val::kValue || out.stage != c.sumsq_stage))
+      return c.fail("the column reduction must see the same value the output tree stores");
     return out;
   }
 };
@@ -677,9 +753,18 @@ class GemmUniversalAdapter {
     d.tile_n = int(std::tuple_element_t<1, TS>::value);
     d.tile_k = int(std::tuple_element_t<2, TS>::value);
     d.flags = ext.flags;
-    if (a.epilogue.ptr_C != nullptr) return Status::kErrorNotSupported;  // no source tensor path
     xefuse::Ctx c;
+    if (a.epilogue.ptr_C != nullptr) {   // a source tensor: only a SrcFetch leaf may consume it
+      using ElementC = typename GemmKernel::CollectiveEpilogue::ElementC;
+      c.has_src = true;
+      c.src.kind = xefuse::Val::kMat;
+      c.src.ptr = a.epilogue.ptr_C;
+      c.src.dtype = xefuse::DType<ElementC>::value;
+      c.src.ld = int64_t(std::get<0>(a.epilogue.dC));
+      c.src.batch = int64_t(std::get<2>(a.epilogue.dC));
+    }
     xefuse::Val v = xefuse::lower<Fusion>(a.epilogue.thread, c);
+    if (c.ok && c.has_src && !c.src_used) c.fail("a source tensor C is given but the tree has no SrcFetch");
     if (!c.ok || v.kind != xefuse::Val::kValue) {
       last_lowering_error() = c.ok ? "the tree does not produce a value" : c.why;
       return Status::kErrorNotSupported;
@@ -714,7 +799,13 @@ class GemmUniversalAdapter {
     xf_gemm_desc d;
     Status s = lower(a, ext_, d);
     if (s != Status::kSuccess) return s;
+    // Callers re-initialize with unchanged arguments inside timing loops (a no-op in the reference,
+    // tests/test_k0a_colred.cpp:353-359): the plan built for exactly these arguments is kept.
+    if (plan_ != nullptr && workspace == planned_workspace_ && std::memcmp(&d, &planned_, sizeof(d)) == 0)
+      return Status::kSuccess;
     release();
+    planned_ = d;
+    planned_workspace_ = workspace;
     // get_workspace_size() is static and cannot see this object's extensions: only when they leave
     // the tile choice alone is the caller's workspace known to be the size the plan needs
     if (workspace != nullptr && ext_.flags == 0) {
@@ -775,6 +866,8 @@ class GemmUniversalAdapter {
   }
 
   xf_plan* plan_ = nullptr;
+  xf_gemm_desc planned_{};             // the lowered arguments plan_ was built from
+  void* planned_workspace_ = nullptr;
   xefuse::Extensions ext_{};
 };
 
