@@ -186,6 +186,9 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_DIAG_NO_LOAD  256 /* timing diagnostics only: skip the TMA operand loads (D is garbage) */
 #define XF_FLAG_DIAG_NO_MMA   512 /* timing diagnostics only: skip the tensor-core MMAs (D is garbage) */
 #define XF_FLAG_DIAG_NO_EPILOGUE 1024 /* timing diagnostics only: drain TMEM, compute and store nothing */
+#define XF_FLAG_NO_PDL      4096 /* launch without programmatic stream serialization: by default the
+                                    kernel's set-up may overlap the tail of the previous kernel of the
+                                    stream; its global reads and writes always wait for that kernel */
 
 typedef struct xf_plan xf_plan;
 

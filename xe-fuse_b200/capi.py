@@ -18,6 +18,7 @@ OUT_FULL, OUT_COMPACT = 0, 1
 FLAG_DIRECT_STORE, FLAG_FORCE_1CTA, FLAG_FORCE_2CTA, FLAG_FORCE_BN128, FLAG_FORCE_BN256 = 1, 2, 4, 8, 16
 FLAG_FORCE_KS1, FLAG_FORCE_KS2 = 32, 64
 FLAG_NO_SPLIT = 128
+FLAG_NO_PDL = 4096
 FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA = 256, 512
 
 STATUS_NAMES = ["XF_SUCCESS", "XF_ERR_MISALIGNED_OPERAND", "XF_ERR_INVALID_DATA_TYPE",

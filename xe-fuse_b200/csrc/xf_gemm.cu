@@ -105,6 +105,7 @@ struct xf_plan {
   const xf::Variant* variant;
   int grid;
   int device;
+  int no_pdl;   // 1: launch without programmatic stream serialization
   char name[64];
 };
 
@@ -454,6 +455,7 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   const int dev = g.dev;
   const Variant* v = g.v;
   plan->variant = v;
+  plan->no_pdl = (d->flags & XF_FLAG_NO_PDL) ? 1 : 0;
   plan->device = dev;
   GemmParams& p = plan->params;
   memset(&p, 0, sizeof(p));
@@ -609,13 +611,17 @@ xf_status xf_gemm_run(xf_plan* plan, void* stream) {
   cfg.blockDim = dim3(384, 1, 1);
   cfg.dynamicSmemBytes = plan->variant->smem;
   cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = plan->variant->ctas;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = plan->variant->ctas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: this kernel's set-up may overlap the tail of the previous
+  // kernel of the stream (the kernel waits for that kernel's completion before any global access)
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = plan->no_pdl ? 1 : 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, plan->variant->fn, plan->params);
   if (e != cudaSuccess) {
     xf::set_error("launch of %s failed: %s", plan->name, cudaGetErrorString(e));

@@ -403,6 +403,15 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   ptx::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
+  // Programmatic dependent launch.  Everything above touched only shared memory, TMEM and the
+  // kernel parameters, so it may run while the previous kernel of the stream is still finishing;
+  // nothing below may: every global read and write of this kernel comes after the wait, which
+  // returns once the previous grid has completed and its memory is visible.  The early trigger
+  // lets the next kernel's CTAs take each SM as soon as this kernel's CTA leaves it.  Both
+  // instructions are no-ops for a launch without the attribute.
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
