@@ -99,7 +99,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
-    def stop(self, t0=None, t1=None):
+    def stop(self, t0=None, t1=None, load_window=None):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
         time.sleep(0.12)
@@ -120,11 +120,20 @@ class ClockSampler:
                     if l and l.split(",")[0].strip().isdigit()]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm = sorted(int(r[0]) for r in rows)
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        # the SM clock under load: samples of the window in which the timed step ran continuously
+        load = []
+        if load_window is not None:
+            for ts, l in self.lines:
+                f = [x.strip() for x in l.split(",")]
+                if load_window[0] <= ts <= load_window[1] and len(f) >= 6 and f[0].isdigit():
+                    load.append(int(f[0]))
+        sm = sorted(load) if load else sorted(int(r[0]) for r in rows)
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons,
-                "samples": len(rows)}
+                "samples": len(rows), "load_samples": len(load),
+                "how": "sm_mhz = median over the untimed repeat of the timed step that follows it; "
+                       "reasons over the whole run"}
 
 
 # ------------------------------------------------------------------------------ synthetic inputs
@@ -499,8 +508,9 @@ def main():
     sampler = ClockSampler(uuid)
     sampler.start()
     time.sleep(0.15)
-    # a long enough region for the clock sampler: repeat the timed block, keep the best-of? No:
-    # EXACTLY `steps` steps are timed; the sampler simply also sees the e2e and unfused loops.
+    # EXACTLY `steps` steps are timed.  That region is milliseconds long, shorter than one
+    # nvidia-smi sample, so the same step is then repeated untimed for about half a second and the
+    # SM clock is read over that window; throttle reasons are collected over the whole run.
     t0w = time.time()
     ms = time_loop(torch, step, args.steps, flush)
     barrier()
@@ -514,6 +524,15 @@ def main():
             raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
     value = flops_total * args.steps / (ms * 1e-3) / 1e12
     ms_per_step = ms / args.steps
+    # the same number of repeats on every rank (ms is the max over ranks): stages may hold collectives
+    load_steps = max(args.steps, min(20000, int(0.5 / max(ms_per_step * 1e-3, 1e-6))))
+    tl0 = time.time()
+    for i in range(load_steps):
+        step()
+        if i % 64 == 63:
+            torch.cuda.synchronize()
+    barrier()
+    tl1 = time.time()
 
     # ---- end to end through the C ABI with host buffers: every step copies its activations and
     # row scales from pinned host memory and reads its whole output back.  Two device buffer sets
@@ -600,7 +619,7 @@ def main():
         unfused = {"value": v_u, "unit": "TFLOP/s", "ms_per_step": ms_u / args.steps,
                    "fused_speedup": value / v_u, "launches_per_step": sum(u["launches"] for u in us)}
         del us, us_rot
-    clocks = sampler.stop(t0w, time.time())
+    clocks = sampler.stop(t0w, time.time(), load_window=(tl0 + 0.1, tl1))
 
     if rank != 0:
         if dist is not None:
