@@ -186,6 +186,9 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_DIAG_NO_LOAD  256 /* timing diagnostics only: skip the TMA operand loads (D is garbage) */
 #define XF_FLAG_DIAG_NO_MMA   512 /* timing diagnostics only: skip the tensor-core MMAs (D is garbage) */
 #define XF_FLAG_DIAG_NO_EPILOGUE 1024 /* timing diagnostics only: drain TMEM, compute and store nothing */
+#define XF_FLAG_SHORT_WAITS 8192 /* bounded waits inside the kernel give up after about a millisecond
+                                    instead of about two seconds (fail fast; also how the give-up
+                                    path is tested) */
 #define XF_FLAG_NO_PDL      4096 /* launch without programmatic stream serialization: by default the
                                     kernel's set-up may overlap the tail of the previous kernel of the
                                     stream; its global reads and writes always wait for that kernel */
@@ -205,7 +208,11 @@ XF_API xf_status xf_gemm_plan_create(const xf_gemm_desc* desc, void* workspace, 
 /* Enqueues one fused launch on `stream` (a cudaStream_t; NULL = default stream).  Re-entrant. */
 XF_API xf_status xf_gemm_run(xf_plan* plan, void* stream);
 /* Reads back (synchronously) the device status word of the plan's last launches:
- * 0 = ok, otherwise the code of the bounded wait that gave up. */
+ * 0 = ok (returns XF_SUCCESS), otherwise the code of the bounded wait that gave up: 1 producer
+ * waiting for a free stage, 2 MMA issuer waiting for operands, 3 MMA issuer waiting for a free
+ * accumulator, 4 epilogue waiting for the accumulator, 5 a K slice waiting for the other slices'
+ * partials (returns XF_ERR_INTERNAL; the outputs of that launch are not valid).  A non-zero code is
+ * reported once: the word and the split counters are cleared so the plan can run again. */
 XF_API xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code);
 /* Name of the kernel variant the plan selected, e.g. "bf16_128x256_cta2_s6". */
 XF_API const char* xf_gemm_plan_kernel_name(const xf_plan* plan);

@@ -111,3 +111,37 @@ def test_small_workspace_falls_back_to_whole_tiles(capi, oracle, cuda):
     from conftest import bf16_bits
     want = oracle.epilogue(oracle.gemm_bf16(d["A"], d["B"]))
     assert pc.compare_bf16(oracle, bf16_bits(D), want)[0] == 0
+
+
+def test_split_wait_gives_up_and_the_plan_recovers(capi, oracle, cuda):
+    """The give-up side of a bounded wait, made on purpose without a fault: the counter a K slice
+    polls for the other slices' partials is set so far below zero that it cannot reach its target;
+    with XF_FLAG_SHORT_WAITS every waiting warp gives up after about a millisecond, the kernel ends
+    normally with code 5 in the status word, the host reads it, and the same plan then runs
+    correctly again."""
+    import torch
+    from conftest import bf16_bits
+    d = pc.make_inputs(oracle, "k1", 512, 2048, 8192, 6)
+    A = torch.from_numpy(d["A"].view(np.int16)).view(torch.bfloat16).to(cuda)
+    B = torch.from_numpy(d["B"].view(np.int16)).view(torch.bfloat16).to(cuda)
+    D = torch.empty((512, 2048), dtype=torch.bfloat16, device=cuda)
+    plan = capi.GemmPlan(A, B, D, flags=capi.FLAG_SHORT_WAITS)
+    assert "ksplit" in plan.kernel_name
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    good = bf16_bits(D).copy()
+    counters = plan.workspace[256:256 + 32].view(torch.int32)   # first split tile, first CTA
+    counters[0] = -1000000                                       # "published" can never reach its target
+    torch.cuda.synchronize()
+    plan.run()
+    torch.cuda.synchronize()                                     # returns: the wait is bounded
+    with pytest.raises(capi.XfError) as e:
+        plan.device_status()
+    assert "device code 5" in str(e.value)
+    assert plan.device_status() == 0                             # reported once, then cleared
+    D.zero_()
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    assert np.array_equal(bf16_bits(D), good)

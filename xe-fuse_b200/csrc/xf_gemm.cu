@@ -473,7 +473,8 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   p.D = d->D; p.ldd = d->ldd; p.batch_d = d->batch_d;
   p.d_dtype = d->dtype_d;
   p.status = reinterpret_cast<int*>(workspace);
-  p.wait_budget = 4000000000LL;  // about two seconds of SM clocks
+  // about two seconds of SM clocks; a millisecond for callers that would rather fail fast
+  p.wait_budget = (d->flags & XF_FLAG_SHORT_WAITS) ? 2000000LL : 4000000000LL;
   const xf_epilogue_desc& e = d->epi;
   p.epi.residual = to_mat(e.residual);
   p.epi.aux_store = to_mat(e.aux_store);
@@ -722,7 +723,9 @@ xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code) {
     return XF_ERR_INTERNAL;
   }
   if (*device_code != 0) {
-    // a launch that gave up may have left the split counters part-way: clear them for the next one
+    // reported once: clear the word, and the split counters a launch that gave up may have left
+    // part-way, so the plan can run again
+    cudaMemset(plan->params.status, 0, 16);
     if (plan->params.split_counters)
       cudaMemset(plan->params.split_counters, 0,
                  reinterpret_cast<char*>(plan->params.split_partials) -
