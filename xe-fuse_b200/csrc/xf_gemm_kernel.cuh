@@ -3,16 +3,21 @@
 //   D = epilogue(A[M,K] * B[K,N])      A row-major (K contiguous), B row-major (N contiguous)
 //
 // One CTA (CTAS == 1) or a pair of CTAs on neighbouring SMs (CTAS == 2, cta_group::2) owns a
-// (128*CTAS) x BN output tile.  Roles inside a 256-thread CTA:
+// (128*CTAS) x BN output tile.  Roles inside a 384-thread CTA:
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A and B stages
 //   warp 1      MMA issuer:   one lane issues tcgen05.mma (kind::f16 / kind::i8) into TMEM
 //   warp 2      TMEM allocator
-//   warps 4-7   epilogue:     tcgen05.ld the accumulator (one row per thread, 32 columns per
-//               load), run the flat epilogue program in registers, stage bf16 rows in swizzled
-//               shared memory and TMA-store them
+//   warps 4-11  epilogue, two warps per TMEM lane quadrant taking alternate 32-column units:
+//               tcgen05.ld the accumulator (one row per thread, 32 columns per load), run the flat
+//               epilogue program in registers, stage bf16 rows in swizzled shared memory and
+//               TMA-store them
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
 // the main loop of tile i+1.  Adjacent output columns (2k, 2k+1) are adjacent registers of one
 // thread, so SwiGLU / GeGLU / RoPE need no cross-lane traffic.
+//
+// Work items are whole tiles, except that the tiles of a partly filled last wave may be cut into K
+// slices (GemmParams::split_s): the slices exchange raw accumulators through global memory and
+// share the finishing work (see the epilogue role).
 //
 // Shared memory per stage: A 128 rows x 128 B (K-major, 128-B swizzle) and B as BN/CTAS columns
 // split into 128-B column groups of KBLK rows each (MN-major, 128-B swizzle), exactly as the TMA
@@ -50,14 +55,13 @@ struct TileCfg {
   static constexpr int THREADS = (4 + EPI_WARPS) * 32;
   static constexpr int EPI_BUFS = 2;                   // staging buffers per epilogue warp
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
-  static constexpr int VEC_BYTES = 0;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_LIMIT = 227 * 1024;
   static constexpr int STAGES_RAW =
-      (SMEM_LIMIT - 1024 - EPI_BYTES - VEC_BYTES - BAR_BYTES) / STAGE_BYTES;
+      (SMEM_LIMIT - 1024 - EPI_BYTES - BAR_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES =
-      1024 + STAGES * STAGE_BYTES + EPI_BYTES + VEC_BYTES + BAR_BYTES;
+      1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;             // double-buffered accumulator
   static_assert(NGRP >= 1, "B tile narrower than one 128-byte column group");
   static_assert(TMEM_COLS == 256 || TMEM_COLS == 512 || TMEM_COLS == 128, "TMEM columns");
@@ -358,8 +362,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
 
   uint8_t* stage_base = smem;
   uint8_t* epi_base = smem + STAGES * C::STAGE_BYTES;
-  float* vec_base = reinterpret_cast<float*>(epi_base + C::EPI_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(vec_base) + C::VEC_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_base + C::EPI_BYTES);
   uint64_t* full_bar = bars;                 // [STAGES]   TMA bytes landed (leader CTA's is used)
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]   MMAs reading the stage have finished
   uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]        accumulator buffer complete
