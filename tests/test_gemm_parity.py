@@ -221,3 +221,35 @@ def test_canary_rows_and_columns_untouched(capi, oracle, cuda):
         want = oracle.epilogue(oracle.gemm_bf16(d["A"], d["B"]), row=d["scale"])
         assert pc.compare_bf16(oracle, bf16_bits(buf[:M, :N].contiguous()), want)[0] == 0
         assert bool((buf[M:, :] == 777.0).all()) and bool((buf[:, N:] == 777.0).all())
+
+
+@pytest.mark.parametrize("flags_name", ["pdl", "no_pdl"])
+def test_dependent_launches_stay_ordered(flags_name, capi, oracle, cuda):
+    """A chain D1 = A*B1, D2 = D1*B2 launched back to back with no host synchronisation, many times
+    over with D1 overwritten in between: with programmatic dependent launch the second kernel's
+    set-up overlaps the first one's tail, but it must not read D1 before the first has finished."""
+    import torch
+    from conftest import bf16_bits
+    M, K, N1, N2 = 256, 512, 1024, 512
+    rng = np.random.default_rng(77)
+    A = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    B1 = oracle.f32_to_bf16((rng.standard_normal((K, N1)) * K ** -0.5).astype(np.float32))
+    B2 = oracle.f32_to_bf16((rng.standard_normal((N1, N2)) * N1 ** -0.5).astype(np.float32))
+    tA, tB1, tB2 = (_t(torch, x, cuda, True) for x in (A, B1, B2))
+    D1 = torch.zeros((M, N1), dtype=torch.bfloat16, device=cuda)
+    D2 = torch.zeros((M, N2), dtype=torch.bfloat16, device=cuda)
+    flags = capi.FLAG_NO_PDL if flags_name == "no_pdl" else 0
+    p1 = capi.GemmPlan(tA, tB1, D1, flags=flags)
+    p2 = capi.GemmPlan(D1, tB2, D2, flags=flags)
+    poison = capi.GemmPlan(tA, tB1, D1, row_scale=torch.zeros(M, device=cuda), flags=flags)   # writes D1 = 0
+    for _ in range(25):
+        poison.run()
+        p1.run()
+        p2.run()
+    torch.cuda.synchronize()
+    assert p1.device_status() == 0 and p2.device_status() == 0
+    d1 = oracle.epilogue(oracle.gemm_bf16(A, B1))
+    want = oracle.epilogue(oracle.gemm_bf16(d1, B2))
+    assert np.array_equal(bf16_bits(D1), d1) or pc.compare_bf16(oracle, bf16_bits(D1), d1)[0] == 0
+    assert pc.compare_bf16(oracle, bf16_bits(D2), oracle.epilogue(oracle.gemm_bf16(bf16_bits(D1), B2)))[0] == 0
+    assert pc.compare_bf16(oracle, bf16_bits(D2), want)[0] == 0

@@ -101,6 +101,17 @@ struct WorkItem {
   int tile, kb0, kb1, slice, split_idx;   // split_idx < 0: whole tile
 };
 
+// Order in which a scheduling unit takes its work items.  Unit u owns items u, u + U, u + 2U, ...;
+// whole tiles come first in that numbering and a K slice, if the unit has one, last (item
+// split_first + u, split_first being a multiple of U).  The unit runs its slice FIRST: all slices
+// of a tile then start together when the kernel starts, and their exchange through global memory
+// (publish, wait, sum) hides behind the main loop of the unit's next tile instead of trailing the
+// kernel.  Maps the loop variable w (u, u + U, ...) to the item to run.
+__device__ __forceinline__ int schedule_item(const GemmParams& p, int w, int unit, int num_units) {
+  if (p.split_s == 0 || unit >= p.total_items - p.split_first || p.split_first == 0) return w;
+  return (w == unit) ? p.split_first + unit : w - num_units;
+}
+
 __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int w) {
   WorkItem it;
   if (p.split_s == 0 || w < p.split_first) {
@@ -422,7 +433,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       bool ok = true;
       for (int w = cluster_idx; w < total_items && ok; w += num_clusters) {
-        const WorkItem wi = decode_item(p, w);
+        const WorkItem wi = decode_item(p, schedule_item(p, w, cluster_idx, num_clusters));
         const TileCoord tc = decode_tile(p, wi.tile);
         const int row0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
         const int col0 = tc.tn * BN + static_cast<int>(cta_rank) * C::BN_CTA;
@@ -471,7 +482,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       int it = 0;
       bool ok = true;
       for (int w = cluster_idx; w < total_items && ok; w += num_clusters, ++it) {
-        const WorkItem wi = decode_item(p, w);
+        const WorkItem wi = decode_item(p, schedule_item(p, w, cluster_idx, num_clusters));
         const int buf = it & 1;
         if (!ptx::mbar_wait(ptx::smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1u, budget)) {
           if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_MMA_TMEM_EMPTY);
@@ -529,7 +540,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         (CTAS == 2) ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0) : ptx::smem_u32(&tempty_bar[0]);
     int it = 0;
     for (int w = cluster_idx; w < total_items; w += num_clusters, ++it) {
-      const WorkItem wi = decode_item(p, w);
+      const WorkItem wi = decode_item(p, schedule_item(p, w, cluster_idx, num_clusters));
       const TileCoord tc = decode_tile(p, wi.tile);
       const int buf = it & 1;
       const int m0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
@@ -563,9 +574,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
 
       // Split tile.  Every slice publishes its raw accumulator rows, then the S slices share the
       // finishing work: slice i sums, in slice order, the 32-output-column units u = i (mod S) of
-      // all S partials and runs the epilogue on them.  A slice item is always the last item of
-      // its CTA and all CTAs of the grid are resident, so the wait below cannot deadlock; it is
-      // bounded all the same.
+      // all S partials and runs the epilogue on them.  A slice is the first item of its CTA and
+      // depends on nothing but the other slices' first items, and all CTAs of the grid are or
+      // become resident, so the wait below cannot deadlock; it is bounded all the same.
       const float* part_base = nullptr;   // non-null: accumulators come from the partials, not TMEM
       int* split_ctr = nullptr;           // [0] warps that have published, [1] warps that are done
       int u_first = half, u_step = 2;

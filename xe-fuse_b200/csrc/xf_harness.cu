@@ -4,6 +4,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <type_traits>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -46,6 +48,8 @@ template <> __device__ __forceinline__ int32_t from_f<int32_t>(float v) { return
 template <> __device__ __forceinline__ int8_t from_f<int8_t>(float v) { return static_cast<int8_t>(v); }
 
 // D[m,n] = alpha * sum_k A[m,k]*B[k,n] + beta*C[m,n]; 32x32 output tile per block, k in order.
+// Each 32-term block of products is summed in fp32 and the blocks in fp64, so the reference carries
+// no accumulation error of its own to speak of (and integer inputs stay exact far beyond 2^24).
 template <class TA, class TC, class TD>
 __global__ void __launch_bounds__(1024) ref_gemm_kernel(const TA* A, long long lda, long long ba, const TA* B,
                                                         long long ldb, long long bb, const TC* C,
@@ -59,20 +63,25 @@ __global__ void __launch_bounds__(1024) ref_gemm_kernel(const TA* A, long long l
   const int n = blockIdx.x * 32 + threadIdx.x;
   A += l * ba; B += l * bb; D += l * bd;
   if (C) C += l * bc;
-  float acc = 0.f;
+  double acc = 0.0;
   for (int k0 = 0; k0 < K; k0 += 32) {
     const int ka = k0 + threadIdx.x, kb = k0 + threadIdx.y;
     sa[threadIdx.y][threadIdx.x] = (m < M && ka < K) ? to_f(A[(long long)m * lda + ka]) : 0.f;
     sb[threadIdx.y][threadIdx.x] = (kb < K && n < N) ? to_f(B[(long long)kb * ldb + n]) : 0.f;
     __syncthreads();
+    float part = 0.f;
 #pragma unroll
-    for (int k = 0; k < 32; ++k) acc = fmaf(sa[threadIdx.y][k], sb[k][threadIdx.x], acc);
+    for (int k = 0; k < 32; ++k) part = fmaf(sa[threadIdx.y][k], sb[k][threadIdx.x], part);
+    acc += static_cast<double>(part);
     __syncthreads();
   }
   if (m < M && n < N) {
-    float v = alpha * acc;
-    if (C && beta != 0.f) v += beta * to_f(C[(long long)m * ldc + n]);
-    D[(long long)m * ldd + n] = from_f<TD>(v);
+    double v = static_cast<double>(alpha) * acc;
+    if (C && beta != 0.f) v += static_cast<double>(beta) * to_f(C[(long long)m * ldc + n]);
+    if constexpr (sizeof(TD) == 4 && !std::is_same<TD, float>::value)
+      D[(long long)m * ldd + n] = static_cast<TD>(llrint(v));   // int32 output: exact
+    else
+      D[(long long)m * ldd + n] = from_f<TD>(static_cast<float>(v));
   }
 }
 
