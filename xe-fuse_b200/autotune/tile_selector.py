@@ -31,7 +31,11 @@ def tile_time_us(bn, eff, K, es):
     return (2.0 + 0.0029 * K * es) * (bn / 256.0) / eff
 
 
-def split_overhead_us(bn):
+def split_overhead_us(bn, whole_waves):
+    """Cost of passing the partial accumulators through L2; partly hidden behind the next tile when
+    the unit has whole tiles to run after its slice."""
+    if whole_waves:
+        return 7.0 if bn == 256 else 5.0
     return 10.0 if bn == 256 else 7.0
 
 
@@ -44,7 +48,7 @@ def split_factor(tiles, units, K, es, bn, ks, eff, compact=False):
     s = min(units // rem, num_kb // MIN_KB_PER_SLICE, MAX_SPLIT, bn // (64 if compact else 32))
     if s < 2:
         return 0
-    return s if tile_time_us(bn, eff, K, es) * (1.0 - 1.0 / s) > split_overhead_us(bn) else 0
+    return s if tile_time_us(bn, eff, K, es) * (1.0 - 1.0 / s) > split_overhead_us(bn, tiles >= units) else 0
 
 
 def native_tile(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT, compact=False, with_split=False):
@@ -59,7 +63,7 @@ def native_tile(M, N, K, dtype="bf16", L=1, sm_count=SM_COUNT, compact=False, wi
         t = tile_time_us(bn, eff, K, es)
         cost = (tiles // units) * t
         if tiles % units:
-            cost += (t / split + split_overhead_us(bn)) if split else t
+            cost += (t / split + split_overhead_us(bn, tiles >= units)) if split else t
         if best is None or cost < best_cost * 0.999:
             best, best_cost, best_split = (bn, ctas, ks), cost, split
     bn, ctas, ks = best

@@ -314,11 +314,16 @@ static double tile_time_us(const Variant& v, int K, int es) {
 // Split-K of the remainder wave.  With T tiles on U scheduling units, the last wave holds
 // T % U tiles and leaves the other units idle; cutting each of those tiles into S K slices fills
 // S times as many units for 1/S of the time, at the price of passing the partial accumulators
-// through L2 (publish, wait for the other slices, sum: about 10 us for a 256-column tile).
-// Returns S, or 0 for whole tiles.
+// through L2 (publish, wait for the other slices, sum).  A unit runs its slice before its whole
+// tiles, so when there are whole waves part of that exchange hides behind the next tile's main
+// loop (measured: about 7 us remain for a 256-column tile); in a problem of less than one wave
+// nothing hides it (about 10 us).  Returns S, or 0 for whole tiles.
 static const int kMaxSplit = 8;
 static const int kMinKbPerSlice = 4;
-static double split_overhead_us(const Variant& v) { return v.bn == 256 ? 10.0 : 7.0; }
+static double split_overhead_us(const Variant& v, bool whole_waves) {
+  if (whole_waves) return v.bn == 256 ? 7.0 : 5.0;
+  return v.bn == 256 ? 10.0 : 7.0;
+}
 static int split_factor(const Variant& v, const xf_gemm_desc* d, int tiles, int units) {
   if (d->flags & XF_FLAG_NO_SPLIT) return 0;
   if (units <= 0) return 0;
@@ -334,7 +339,7 @@ static int split_factor(const Variant& v, const xf_gemm_desc* d, int tiles, int 
   if (s > units_per_tile) s = units_per_tile;
   if (s < 2) return 0;
   const double t = tile_time_us(v, d->K, es);
-  return t * (1.0 - 1.0 / s) > split_overhead_us(v) ? s : 0;
+  return t * (1.0 - 1.0 / s) > split_overhead_us(v, tiles >= units) ? s : 0;
 }
 
 // Picks the CTA tile.  The caller's TileShape (an Intel Xe work-group tile) is only a hint; the
@@ -359,7 +364,7 @@ static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
     const int split = split_factor(v, d, tiles, units);
     const double t = tile_time_us(v, d->K, es);
     double cost = (tiles / units) * t;
-    if (tiles % units) cost += split ? t / split + split_overhead_us(v) : t;
+    if (tiles % units) cost += split ? t / split + split_overhead_us(v, tiles >= units) : t;
     if (!best || cost < best_cost * 0.999) {
       best = &v;
       best_cost = cost;
