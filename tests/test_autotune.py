@@ -47,3 +47,55 @@ def test_selector_mirrors_the_library_choice(capi, cuda):
             plan = capi.GemmPlan(A, B, D)
             # the library's name also carries the pipeline depth ("_s3"), which the mirror leaves out
             assert re.sub(r"_s\d+", "", plan.kernel_name) == ts.kernel_name(M, N, K, dt, sm_count=sms), (M, N, K, dt)
+
+
+def test_split_planner_invariants():
+    """The Python mirror of the planner over a sweep of shapes: a split factor is 0 or 2..8, leaves
+    at least 4 K blocks per slice, never creates more slice items than scheduling units, and each
+    slice finishes whole 32-output-column units of its tile."""
+    ts = _selector()
+    import itertools
+    seen_split = 0
+    for M, N, K in itertools.product([128, 512, 2048, 4096, 8192], [256, 1024, 3584, 7168, 28672],
+                                     [256, 1024, 4096, 14336]):
+        for dt, es, variants in (("bf16", 2, ts.BF16_VARIANTS), ("s8", 1, ts.S8_VARIANTS)):
+            rows, bn, ctas, kstage, split = ts.native_tile(M, N, K, dt, with_split=True)
+            units = ts.SM_COUNT // ctas
+            tiles = -(-M // rows) * -(-N // bn)
+            if split:
+                seen_split += 1
+                num_kb = -(-K // kstage)
+                assert 2 <= split <= 8 and num_kb // split >= 4, (M, N, K, dt, split)
+                assert (tiles % units) * split <= units
+                assert split <= bn // 32
+            else:
+                assert split == 0
+    assert seen_split > 20
+
+
+def test_work_item_order_covers_every_item_once():
+    """Model of the kernel's schedule (schedule_item in csrc/xf_gemm_kernel.cuh): unit u runs items
+    u, u+U, ...; a unit that owns a K slice runs it first.  Every whole tile and every slice is run
+    exactly once, and a unit's slice comes before all of its whole tiles."""
+    def order(unit, U, split_first, total_items, split_s):
+        out = []
+        for w in range(unit, total_items, U):
+            if split_s == 0 or unit >= total_items - split_first or split_first == 0:
+                out.append(w)
+            else:
+                out.append(split_first + unit if w == unit else w - U)
+        return out
+    for T, U, S in [(224, 74, 8), (448, 74, 8), (1792, 74, 4), (256, 74, 2), (32, 74, 2), (1, 148, 8), (75, 74, 8),
+                    (148, 148, 0), (300, 148, 0)]:
+        rem = T % U
+        split_tiles = rem if S else 0
+        split_first = T - split_tiles
+        total_items = split_first + split_tiles * max(S, 1)
+        units = min(total_items, U)
+        ran = []
+        for u in range(units):
+            o = order(u, units, split_first, total_items, S)
+            ran += o
+            slices = [w for w in o if S and w >= split_first]
+            assert len(slices) <= 1 and (not slices or o[0] == slices[0]), (T, U, S, u, o)
+        assert sorted(ran) == list(range(total_items)), (T, U, S)
