@@ -19,7 +19,7 @@ CPP = os.path.join(ROOT, "tests", "cpp")
 BUILD = os.path.join(CPP, "build")
 FE = os.path.join(ROOT, "xe-fuse_b200", "include")
 LIBDIR = os.path.join(ROOT, "xe-fuse_b200")
-REF = "/root/reference"
+REF = os.environ.get("XEFUSE_REFERENCE_ROOT", "/root/reference")   # a checkout of the reference, if any
 CUDA = "/usr/local/cuda"
 
 

@@ -1,4 +1,4 @@
-"""Parity at the BASELINE configurations' full sizes, where the CPU oracle cannot redo the whole
+"""Parity at the full sizes of the five benchmark configurations, where the CPU oracle cannot redo the whole
 GEMM in seconds.  Each case checks (a) sampled rows -- first/last row of CTA tiles plus random
 ones -- element by element against the oracle, and (b) size-independent properties over the whole
 output: exact row/column checksums of the int32 accumulator, the two output layouts of one kernel

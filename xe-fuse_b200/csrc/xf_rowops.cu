@@ -127,7 +127,20 @@ __global__ void __launch_bounds__(256) rmsnorm_plain_kernel(__nv_bfloat16* out, 
 }
 
 __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
-__device__ __forceinline__ float gelu_f(float g) { return g * 0.5f * (1.0f + erff(g * 0.7071067811865475f)); }
+// erf-GeLU, g * 0.5 * (1 + erf(g / sqrt 2)), with erf from the five-term rational approximation of
+// Abramowitz & Stegun 7.1.26 (absolute error below 1.5e-7): 1 - erf(z) = P(t) exp(-z^2),
+// t = 1 / (1 + p z), z >= 0.  For negative g the factor 1 + erf is formed directly as P(t) exp(-z^2),
+// so the far tail does not cancel.  A third of the instructions of erff().
+__device__ __forceinline__ float gelu_f(float g) {
+  const float z = fabsf(g) * 0.7071067811865475f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  const float pe = p * t * __expf(-z * z);         // 1 - erf(z)
+  return g * 0.5f * (g >= 0.0f ? 2.0f - pe : pe);
+}
 
 // out[m, i] = act(in[m, i]) * in[m, d + i]; in is [M, 2d] (gate half, then up half), out [M, d].
 // VEC: 8 columns per thread per step (16-byte loads and stores).  The reference's pipelines call
