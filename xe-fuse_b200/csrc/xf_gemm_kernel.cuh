@@ -795,7 +795,13 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
-    if (lane == 0) ptx::tma_store_wait_all<0>();
+    // Before the CTA may exit its staging buffers must have been read by the bulk stores; the
+    // writes themselves complete with the grid.  Stores into another GPU's memory are waited for
+    // in full: the host-side barrier that follows the kernel tells the peers their data has landed.
+    if (lane == 0) {
+      if (p.num_d_peer > 0) ptx::tma_store_wait_all<0>();
+      else ptx::tma_store_wait_read<0>();
+    }
   }
 
   // ------------------------------------------------------------------ teardown
