@@ -409,6 +409,9 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1, chained stages: all-gather fused into the producer's epilogue "
                          "(peer stores) or a separate ncclAllGather")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="single-GPU runs only: run ONE rank's column shard of an N-way split alone "
+                         "(the kernel a rank of --gpus N launches), e.g. to profile it; not a job figure")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-unfused", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -445,7 +448,12 @@ def main():
     peaks = load_peaks()
     l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
 
-    host = [gen_stage_host(st, rank, world, seed=2024 + i) for i, st in enumerate(stages)]
+    shape_world = world
+    if args.shard_of > 1:
+        if world != 1 or any(len(st) > 5 and st[5] == "chain" for st in stages):
+            raise SystemExit("bench.py --shard-of needs a single process and a workload without a gather")
+        shape_world = args.shard_of
+    host = [gen_stage_host(st, rank, shape_world, seed=2024 + i) for i, st in enumerate(stages)]
 
     def build_set(share_from=None):
         """One set of per-step buffers + plans for all stages.  When a stage feeds a chained
@@ -673,7 +681,9 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "s8" if is_s8 else "bf16", "data": "synthetic",
         "config": {"workload": DESCR[args.workload],
-                   "sharding": (f"weight columns N split {world}-way, activations and row scales replicated, no collective inside a stage"
+                   "sharding": ((f"ONE rank's shard of a {shape_world}-way column split, run alone; value is this GPU's rate; "
+                                 if shape_world != world else "") +
+                                f"weight columns N split {shape_world}-way, activations and row scales replicated, no collective inside a stage"
                                 + ((f"; gate/up output shards all-gathered into K slabs for the down projection "
                                     f"({'peer stores from the epilogue' if args.gather == 'fused' else 'ncclAllGather'})")
                                    if world > 1 and any(s["chain"] for s in gpu) else "")),
