@@ -189,6 +189,9 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_SHORT_WAITS 8192 /* bounded waits inside the kernel give up after about a millisecond
                                     instead of about two seconds (fail fast; also how the give-up
                                     path is tested) */
+#define XF_FLAG_NO_TAIL_HELP 32768 /* the producer / MMA / allocator warps do not join the epilogue of a
+                                    CTA's last tile (by default they do, as a third worker per TMEM
+                                    quadrant: that epilogue has no main loop left to hide behind) */
 #define XF_FLAG_NO_PDL      4096 /* launch without programmatic stream serialization: by default the
                                     kernel's set-up may overlap the tail of the previous kernel of the
                                     stream; its global reads and writes always wait for that kernel */

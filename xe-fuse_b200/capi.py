@@ -20,6 +20,7 @@ FLAG_FORCE_KS1, FLAG_FORCE_KS2 = 32, 64
 FLAG_NO_SPLIT = 128
 FLAG_NO_PDL = 4096
 FLAG_SHORT_WAITS = 8192
+FLAG_NO_TAIL_HELP = 32768
 FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA = 256, 512
 
 STATUS_NAMES = ["XF_SUCCESS", "XF_ERR_MISALIGNED_OPERAND", "XF_ERR_INVALID_DATA_TYPE",

@@ -499,7 +499,8 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
                             (d->batch_d * 2) % 16 == 0 && !(d->flags & XF_FLAG_DIRECT_STORE);
   p.direct_store = tma_store_ok ? 0 : 1;
   p.diag = ((d->flags & XF_FLAG_DIAG_NO_LOAD) ? 1 : 0) | ((d->flags & XF_FLAG_DIAG_NO_MMA) ? 2 : 0) |
-           ((d->flags & XF_FLAG_DIAG_NO_EPILOGUE) ? 4 : 0) | ((d->flags & 2048) ? 8 : 0);
+           ((d->flags & XF_FLAG_DIAG_NO_EPILOGUE) ? 4 : 0) | ((d->flags & 2048) ? 8 : 0) |
+           ((d->flags & XF_FLAG_NO_TAIL_HELP) ? 16 : 0);
 
   const CUtensorMapDataType dt =
       d->dtype_ab == XF_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;

@@ -379,6 +379,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]        accumulator buffer complete
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]    accumulator buffer drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* tail_bar = bars + 2 * STAGES + 6;    // [1]        the CTA's last accumulator is complete
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -400,6 +401,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(ptx::smem_u32(&tfull_bar[b]), 1);
+      if (b == 0) ptx::mbar_init(ptx::smem_u32(tail_bar), 1);
       ptx::mbar_init(ptx::smem_u32(&tempty_bar[b]), C::EPI_WARPS * CTAS);
     }
     ptx::fence_mbar_init();
@@ -521,17 +523,30 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t tb = ptx::smem_u32(&tfull_bar[buf]);
         ptx::umma_commit<CTAS>(tb);
         if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(tb, 1));
+        if (w + num_clusters >= total_items) {   // last item: also wake the warps that help with it
+          const uint32_t lb = ptx::smem_u32(tail_bar);
+          ptx::umma_commit<CTAS>(lb);
+          if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(lb, 1));
+        }
       }
     }
-  } else if (warp >= 4) {
-    // ------------------------------------------------------------------ epilogue (8 warps)
-    // Two warps share each TMEM lane quadrant and take alternate 32-output-column units of the
-    // tile, so every scheduler of the SM holds two epilogue warps whose latencies overlap.
-    const int ew = warp - 4;
-    const int q = ew & 3;                   // TMEM lane quadrant this warp may read
-    const int half = ew >> 2;               // which of the two warps of the quadrant
+  }
+  __syncwarp();
+  {
+    // ------------------------------------------------------------------ epilogue
+    // Warps 4-11: two warps share each TMEM lane quadrant and take alternate 32-output-column
+    // units of the tile, so every scheduler of the SM holds two epilogue warps whose latencies
+    // overlap.  Warps 0-3 have finished their own roles by the time the CTA's LAST tile is
+    // accumulated, and that tile's epilogue has no main loop left to hide behind: they join it as
+    // a third worker per quadrant (a warp may read the TMEM lanes of quadrant warp % 4), staging
+    // their stores in the then idle pipeline stages.
+    const bool helper = warp < 4;
+    const int ew = helper ? warp : warp - 4;
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = helper ? 2 : ew >> 2;  // which worker of the quadrant
     const EpiParams& e = p.epi;
-    uint8_t* stg = epi_base + ew * (C::EPI_BUFS * C::EPI_BUF_BYTES);
+    uint8_t* stg = helper ? stage_base + warp * (C::EPI_BUFS * C::EPI_BUF_BYTES)
+                          : epi_base + ew * (C::EPI_BUFS * C::EPI_BUF_BYTES);
     int sidx = 0;
     const bool compact = e.compact != 0;
     const int n_out = compact ? (p.N >> 1) : p.N;
@@ -541,6 +556,8 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     int it = 0;
     for (int w = cluster_idx; w < total_items; w += num_clusters, ++it) {
       const WorkItem wi = decode_item(p, schedule_item(p, w, cluster_idx, num_clusters));
+      // the CTA's last item, if it is a whole tile, is shared three ways per quadrant
+      const bool shared3 = (w + num_clusters >= total_items) && wi.split_idx < 0 && !(p.diag & 16);
       const TileCoord tc = decode_tile(p, wi.tile);
       const int buf = it & 1;
       const int m0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
@@ -549,10 +566,19 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       float rs = 1.0f;
-      if (e.row_scale.enabled && row_ok)
+      if (e.row_scale.enabled && row_ok && (!helper || shared3))
         rs = load_vec_elem(e.row_scale, static_cast<long long>(l) * e.row_scale.batch_stride + row);
 
-      if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[buf]), (it >> 1) & 1, budget)) {
+      // Helpers wait on a barrier of their own that completes once, with the CTA's last
+      // accumulator: the two-phase barriers of the accumulator buffers name a phase by one parity
+      // bit, which a warp that has not followed them phase by phase cannot wait on safely.
+      if (helper) {
+        if (!shared3) continue;
+        if (!ptx::mbar_wait(ptx::smem_u32(tail_bar), 0u, budget)) {
+          if (p.status && lane == 0) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_EPI_TMEM_FULL);
+          break;
+        }
+      } else if (!ptx::mbar_wait(ptx::smem_u32(&tfull_bar[buf]), (it >> 1) & 1, budget)) {
         if (p.status && lane == 0) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_EPI_TMEM_FULL);
         break;
       }
@@ -566,10 +592,11 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       const int nunits = (nsub + slices_per_unit - 1) / slices_per_unit;
       bool released = false;
       auto release_tmem = [&]() {   // this warp has read its last slice of the accumulator buffer
+        released = true;
+        if (helper) return;         // helpers only see the last tile: nobody waits for its buffer
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
-        released = true;
       };
 
       // Split tile.  Every slice publishes its raw accumulator rows, then the S slices share the
@@ -579,7 +606,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       // become resident, so the wait below cannot deadlock; it is bounded all the same.
       const float* part_base = nullptr;   // non-null: accumulators come from the partials, not TMEM
       int* split_ctr = nullptr;           // [0] warps that have published, [1] warps that are done
-      int u_first = half, u_step = 2;
+      int u_first = half, u_step = shared3 ? 3 : 2;
       if (wi.split_idx >= 0) {
         const size_t slab = static_cast<size_t>(C::BM) * BN;   // words per (slice, CTA)
         // slab layout [32-column slice][16-byte chunk][row]: the 32 lanes of a store are contiguous
@@ -630,7 +657,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
 
       for (int u = u_first; u < nunits; u += u_step) {
         uint32_t pk[16];
-        const bool last_unit = (u + 2 >= nunits);
+        const bool last_unit = (u + u_step >= nunits);
         int out_col0 = 0;
         bool stored_direct = false;
 #pragma unroll 1
