@@ -10,7 +10,7 @@
 //   warps 4-11  epilogue, two warps per TMEM lane quadrant taking alternate 32-column units:
 //               tcgen05.ld the accumulator (one row per thread, 32 columns per load), run the flat
 //               epilogue program in registers, stage bf16 rows in swizzled shared memory and
-//               TMA-store them
+//               TMA-store them; warps 0-3 join them for the CTA's last tile
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
 // the main loop of tile i+1.  Adjacent output columns (2k, 2k+1) are adjacent registers of one
 // thread, so SwiGLU / GeGLU / RoPE need no cross-lane traffic.
