@@ -527,9 +527,10 @@ def main():
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    for s in gpu:
-        if s["plan"].device_status() != 0:
-            raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
+    for g in rot:
+        for s in g:
+            if s["plan"].device_status() != 0:
+                raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
     value = flops_total * args.steps / (ms * 1e-3) / 1e12
     ms_per_step = ms / args.steps
     # the same number of repeats on every rank (ms is the max over ranks): stages may hold collectives
