@@ -10,19 +10,30 @@ output [4096,14336] bf16).  With N GPUs the weight columns are sharded N-ways (a
 per-row scales replicated, nothing exchanged inside a stage), so total work is fixed: strong
 scaling.  Prints ONE JSON line on rank 0.
 
-  value     whole-job TFLOP/s (2*M*N*K per GEMM), inputs resident in HBM, CUDA-event timed,
-            max over ranks
-  e2e       the same metric through the C ABI with HOST buffers: every step copies the step's
-            activations + row scales host->device from pinned memory and the output device->host
-  roofline  tensor-core bound: achieved 2MNK / average launch time against the measured bf16 peak
+  value       whole-job TFLOP/s (2*M*N*K per GEMM), inputs resident in HBM, CUDA-event timed,
+              max over ranks
+  value_sustained
+              the same step repeated back to back for about half a second (the part then sits on
+              its power cap), with the SM clock sampled over that window
+  e2e         the same metric through the C ABI with HOST buffers: every step copies the step's
+              activations + row scales host->device from pinned memory and the output device->host
+  roofline    tensor-core bound: achieved 2MNK / average launch time against the measured bf16
+              peak; int8 against an int8 peak measured in the same run
+  all_configs (1 GPU, default workload) the other BASELINE configurations, device-timed, with
+              their unfused arm
+  pipeline    (N > 1, default workload) the Llama-3-70B layer chain, whose gate/up -> down hand-off
+              is the path's one collective: all-gather fused into the producer's epilogue (peer
+              stores) and as a separate ncclAllGather, plus a bit-for-bit check of one against
+              the other
   cpu_baseline / --impl reference
-            the CPU oracle (a port of the reference's formulas; the reference has no CPU or CUDA
-            implementation of its own) timed on the host cores on a bounded row-sample
+              the CPU oracle (a port of the reference's formulas; the reference has no CPU or CUDA
+              implementation of its own) timed on the host cores on a bounded row-sample
 """
 import argparse
 import json
 import math
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -54,14 +65,7 @@ DESCR = {
     "pipeline": "Llama-3-70B layer GEMM chain M=8192: QKV k4v2 (K=8192,N=10240), O k0a (8192,8192), "
                 "gate/up k2 (K=8192,N=57344), down k0a (K=28672,N=8192)",
 }
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's kernel, from the
-# ncu captures summarised under profiles/ (full-size workloads, one GPU).
-NCU_DRAM_BYTES_PER_LAUNCH = {
-    "k2": 507_871_488 + 108_579_584,       # profiles/gemm_evt_kernel_bf16_256x256_cta2_k128__k2_*.md
-    "w8a8": 1_990_824_000 + 129_954_816,   # profiles/gemm_evt_kernel_s8_256x256_cta2_k256__w8a8_*.md
-}
+OTHER_CONFIGS = ["k1", "k4v2_q", "k4v2_kv", "w8a8", "pipeline"]
 
 
 def load_peaks():
@@ -71,6 +75,20 @@ def load_peaks():
         return {"bf16": d["bf16_tflops"], "bf16_sustained": d.get("bf16_tflops_sustained"),
                 "hbm": d["hbm_gbs"], "src": "measured"}
     return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "src": "fallback"}
+
+
+def load_traffic():
+    """DRAM bytes per launch of each workload's kernel from the profiler summaries: the one table of
+    the form `| workload | dram read B | dram write B | ...` in profiles/dram_traffic.md."""
+    out = {}
+    p = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    if not os.path.exists(p):
+        return out
+    for line in open(p):
+        m = re.match(r"\|\s*(\w+)\s*\|\s*([\d_,]+)\s*\|\s*([\d_,]+)\s*\|", line)
+        if m:
+            out[m.group(1)] = int(re.sub(r"[_,]", "", m.group(2))) + int(re.sub(r"[_,]", "", m.group(3)))
+    return out
 
 
 # ------------------------------------------------------------------------------ clocks sampler
@@ -99,7 +117,16 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
-    def stop(self, t0=None, t1=None, load_window=None):
+    def median_sm(self, t0, t1):
+        v = []
+        for ts, l in list(self.lines):
+            f = [x.strip() for x in l.split(",")]
+            if t0 <= ts <= t1 and len(f) >= 6 and f[0].isdigit():
+                v.append(int(f[0]))
+        v.sort()
+        return (v[len(v) // 2], len(v)) if v else (None, 0)
+
+    def stop(self, load_window=None):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
         time.sleep(0.12)
@@ -108,97 +135,93 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        rows = []
-        for ts, l in self.lines:
-            if t0 is not None and not (t0 - 0.05 <= ts <= t1 + 0.1):
-                continue
-            f = [x.strip() for x in l.split(",")]
-            if len(f) >= 6 and f[0].isdigit():
-                rows.append(f)
-        if not rows:
-            rows = [[x.strip() for x in l.split(",")] for _, l in self.lines
-                    if l and l.split(",")[0].strip().isdigit()]
+        rows = [[x.strip() for x in l.split(",")] for _, l in self.lines
+                if l and l.split(",")[0].strip().isdigit() and len(l.split(",")) >= 6]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
-        # the SM clock under load: samples of the window in which the timed step ran continuously
-        load = []
+        sm, nload = (None, 0)
         if load_window is not None:
-            for ts, l in self.lines:
-                f = [x.strip() for x in l.split(",")]
-                if load_window[0] <= ts <= load_window[1] and len(f) >= 6 and f[0].isdigit():
-                    load.append(int(f[0]))
-        sm = sorted(load) if load else sorted(int(r[0]) for r in rows)
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons,
-                "samples": len(rows), "load_samples": len(load),
-                "how": "sm_mhz = median over the untimed repeat of the timed step that follows it; "
-                       "reasons over the whole run"}
+            sm, nload = self.median_sm(*load_window)
+        if sm is None:
+            s = sorted(int(r[0]) for r in rows)
+            sm = s[len(s) // 2]
+        return {"sm_mhz": sm, "sm_max_mhz": int(rows[0][1]), "reasons": reasons,
+                "samples": len(rows), "load_samples": nload,
+                "how": "sm_mhz = median over the sustained repeat of the timed step; reasons over the whole run"}
 
 
 # ------------------------------------------------------------------------------ synthetic inputs
-def gen_stage_host(stage, rank, world, seed):
-    """Seeded host tensors of one stage for this rank's column shard (pinned where copied per step)."""
+def gen_stage(stage, rank, world, seed, dev, host_x=True):
+    """Seeded synthetic tensors of one stage for this rank's column shard.  Activations and row
+    scales are made on the host (pinned: the end-to-end arm copies them every step) unless
+    host_x is False; weights, per-column vectors and tables are made on the device."""
     import torch
     preset, M, N, K, dt = stage[:5]
     chain = len(stage) > 5 and stage[5] == "chain"
     assert N % world == 0
     Ns = N // world
     g = torch.Generator().manual_seed(seed)
-    gw = torch.Generator().manual_seed(seed * 7919 + 13 * rank + 1)   # per-shard weight stream
-    h = {}
+    gd = torch.Generator(device=dev).manual_seed(seed * 7919 + 13 * rank + 1)   # per-shard weight stream
+    h = {"X": None, "R": None}
+
+    def randn_dev(*shape):
+        return torch.randn(*shape, generator=gd, device=dev, dtype=torch.float32)
+
+    def bounded_rows(fn, rows):      # weights in row blocks: bounded fp32 temporaries
+        for k0 in range(0, rows, 4096):
+            fn(k0, min(rows, k0 + 4096))
+
     if dt == "bf16":
-        if chain:                      # activations come from the previous stage, on the device
-            h["X"], h["R"] = None, None
-        else:
-            X = torch.randn(M, K, generator=g, dtype=torch.float32)
-            h["R"] = torch.rsqrt((X * X).mean(dim=1) + 1e-6).contiguous()    # fp32 on the host
+        if not chain:
+            if host_x:
+                X = torch.randn(M, K, generator=g, dtype=torch.float32)
+            else:
+                X = torch.randn(M, K, generator=torch.Generator(device=dev).manual_seed(seed), device=dev)
+            h["R"] = torch.rsqrt((X * X).mean(dim=1) + 1e-6).contiguous()    # fp32
             h["X"] = X.to(torch.bfloat16)
-        W = torch.empty(K, Ns, dtype=torch.bfloat16)
-        for k0 in range(0, K, 4096):                                      # bounded temporaries
-            k1 = min(K, k0 + 4096)
-            W[k0:k1] = (torch.randn(k1 - k0, Ns, generator=gw) * K ** -0.5).to(torch.bfloat16)
+        W = torch.empty(K, Ns, dtype=torch.bfloat16, device=dev)
+        bounded_rows(lambda a, b: W[a:b].copy_((randn_dev(b - a, Ns) * K ** -0.5).to(torch.bfloat16)), K)
         h["W"] = W
     else:
-        X = torch.randn(M, K, generator=g, dtype=torch.float32).to(torch.bfloat16).float()
+        gx = g if host_x else torch.Generator(device=dev).manual_seed(seed)
+        X = torch.randn(M, K, generator=gx, dtype=torch.float32,
+                        device="cpu" if host_x else dev).to(torch.bfloat16).float()
         st = X.abs().amax(dim=1) / 127.0 + 1e-8                          # per-token absmax
         h["X"] = torch.clamp(torch.round(X / st[:, None]), -128, 127).to(torch.int8)
         h["R"] = st.contiguous()
-        W = torch.empty(K, Ns, dtype=torch.int8)
-        sc = torch.zeros(Ns)
-        Wf = torch.empty(K, Ns, dtype=torch.bfloat16)
-        for k0 in range(0, K, 4096):
-            k1 = min(K, k0 + 4096)
-            Wf[k0:k1] = (torch.randn(k1 - k0, Ns, generator=gw) * K ** -0.5).to(torch.bfloat16)
+        Wf = torch.empty(K, Ns, dtype=torch.bfloat16, device=dev)
+        bounded_rows(lambda a, b: Wf[a:b].copy_((randn_dev(b - a, Ns) * K ** -0.5).to(torch.bfloat16)), K)
         sc = Wf.float().abs().amax(dim=0) / 127.0 + 1e-8                  # per-channel absmax
-        for k0 in range(0, K, 4096):
-            k1 = min(K, k0 + 4096)
-            W[k0:k1] = torch.clamp(torch.round(Wf[k0:k1].float() / sc[None, :]), -128, 127).to(torch.int8)
+        W = torch.empty(K, Ns, dtype=torch.int8, device=dev)
+        bounded_rows(lambda a, b: W[a:b].copy_(
+            torch.clamp(torch.round(Wf[a:b].float() / sc[None, :]), -128, 127).to(torch.int8)), K)
+        del Wf
         h["W"] = W
         h["sc"] = sc.contiguous()
-        h["bias"] = (torch.randn(Ns, generator=gw) * 0.02).to(torch.bfloat16)
+        h["bias"] = (randn_dev(Ns) * 0.02).to(torch.bfloat16)
     if preset == "k0a":
-        h["residual"] = torch.randn(M, Ns, generator=gw).to(torch.bfloat16)
-        h["gamma"] = (1.0 + 0.02 * torch.randn(Ns, generator=gw)).contiguous()
+        h["residual"] = randn_dev(M, Ns).to(torch.bfloat16)
+        h["gamma"] = (1.0 + 0.02 * randn_dev(Ns)).contiguous()
     if preset == "k4v2":
-        pos = torch.arange(M, dtype=torch.float32)[:, None]
-        i = torch.arange(64, dtype=torch.float32)[None, :]
-        ang = pos * torch.pow(torch.tensor(500000.0), -2.0 * i / 128.0)
-        cs = torch.empty(M, 128)
+        pos = torch.arange(M, dtype=torch.float32, device=dev)[:, None]
+        i = torch.arange(64, dtype=torch.float32, device=dev)[None, :]
+        ang = pos * torch.pow(torch.tensor(500000.0, device=dev), -2.0 * i / 128.0)
+        cs = torch.empty(M, 128, device=dev)
         cs[:, 0::2] = torch.cos(ang)
         cs[:, 1::2] = torch.sin(ang)
         h["cos_sin"] = cs.contiguous()
-    if h["X"] is not None:
-        h["X"] = h["X"].contiguous().pin_memory() if torch.cuda.is_available() else h["X"].contiguous()
-        h["R"] = h["R"].pin_memory() if torch.cuda.is_available() else h["R"]
+    if h["X"] is not None and host_x:
+        h["X"] = h["X"].contiguous().pin_memory()
+        h["R"] = h["R"].pin_memory()
     return h
 
 
 def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=None, consume=None):
     """Device buffers + the fused plan of one stage.  With `share` (an earlier build of the same
     stage) the static operands (weights, per-column vectors, tables) are reused and only the
-    per-step buffers (activations, row scales, output) are new: the second buffer set of the
-    pipelined end-to-end loop."""
+    per-step buffers (activations, row scales, output) are new."""
     import torch
     preset, M, N, K, dt = stage[:5]
     chain = len(stage) > 5 and stage[5] == "chain"
@@ -219,9 +242,11 @@ def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=
             a_k_slabs = True
         s["R"] = None
     else:
-        s["X"] = h["X"].to(dev, non_blocking=True)
-        s["R"] = h["R"].to(dev, non_blocking=True)
-    s["W"] = share["W"] if share else h["W"].to(dev)
+        s["X"] = h["X"].to(dev, non_blocking=True) if h["X"].device != dev or share else h["X"]
+        s["R"] = h["R"].to(dev, non_blocking=True) if h["R"].device != dev or share else h["R"]
+        if share and s["X"].data_ptr() == h["X"].data_ptr():   # device-made inputs: a private copy per set
+            s["X"], s["R"] = h["X"].clone(), h["R"].clone()
+    s["W"] = share["W"] if share else h["W"]
     kw = {}
     n_out = Ns
     if preset == "k1":
@@ -230,15 +255,13 @@ def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=
         kw = dict(row_scale=s["R"], pair="swiglu", compact=True)
         n_out = Ns // 2
     elif preset == "k4v2":
-        s["cos_sin"] = share["cos_sin"] if share else h["cos_sin"].to(dev)
+        s["cos_sin"] = h["cos_sin"]
         kw = dict(row_scale=s["R"], pair="rope", cos_sin=s["cos_sin"], cos_sin_period=128)
     elif preset == "k0a":
-        s["residual"] = share["residual"] if share else h["residual"].to(dev)
-        s["gamma"] = share["gamma"] if share else h["gamma"].to(dev)
+        s["residual"], s["gamma"] = h["residual"], h["gamma"]
         kw = dict(residual=s["residual"], col_scale=s["gamma"])
     elif preset == "w8a8":
-        s["sc"] = share["sc"] if share else h["sc"].to(dev)
-        s["bias"] = share["bias"] if share else h["bias"].to(dev)
+        s["sc"], s["bias"] = h["sc"], h["bias"]
         kw = dict(row_scale=s["R"], col_scale=s["sc"], bias=s["bias"])
     if gather is not None:             # D is this rank's slab of the symmetric gathered buffer
         s["D"] = gather.local_shard
@@ -247,7 +270,7 @@ def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=
         s["D"] = torch.empty(M, n_out, dtype=torch.bfloat16, device=dev)
     s["plan"] = capi.GemmPlan(s["X"], s["W"], s["D"], a_k_slabs=a_k_slabs, **kw)
     s["flops"] = 2.0 * M * Ns * K
-    s["h2d_bytes"] = 0 if chain else h["X"].numel() * h["X"].element_size() + h["R"].numel() * 4
+    s["h2d_bytes"] = 0 if chain else s["X"].numel() * s["X"].element_size() + s["R"].numel() * 4
     s["d2h_bytes"] = s["D"].numel() * 2
     s["bytes_resident"] = ((0 if chain and world == 1 else s["X"].numel() * s["X"].element_size())
                            + s["W"].numel() * s["W"].element_size()
@@ -272,7 +295,7 @@ def build_unfused(capi, s, dev):
         u["launches"] = 3
     else:
         u["out"] = torch.empty(M, Ns, dtype=torch.bfloat16, device=dev)
-        u["plan"] = capi.GemmPlan(s["X"], s["W"], u["out"], a_k_slabs="gather_from" in s)
+        u["plan"] = capi.GemmPlan(s["X"], s["W"], u["out"], a_k_slabs="gather_from" in s or "barrier" in s)
         if preset == "k1":
             u["post"] = lambda: capi.sa_scale_rows(u["out"], s["R"])
             u["launches"] = 2
@@ -291,36 +314,339 @@ def build_unfused(capi, s, dev):
     return u
 
 
-def time_loop(torch, fn, steps, flush=None):
-    """CUDA-event time of `steps` calls on the current stream, in ms.  With `flush`, a buffer larger
-    than L2 is overwritten before every step and only the steps are timed."""
-    if flush is None:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1)
-    evs = []
+def time_loop(torch, fn, steps):
+    """CUDA-event time of `steps` back-to-back calls on the current stream, in ms."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     for _ in range(steps):
-        flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
         fn()
-        b.record()
-        evs.append((a, b))
+    e1.record()
     torch.cuda.synchronize()
-    return sum(a.elapsed_time(b) for a, b in evs)
+    return e0.elapsed_time(e1)
+
+
+# ------------------------------------------------------------------------------ one workload on the GPU(s)
+class Workload:
+    """Buffers, plans and timed loops of one workload on this rank."""
+
+    def __init__(self, ctx, name, gather="fused", shard_of=0, host_x=True):
+        import torch
+        self.ctx, self.name, self.gather = ctx, name, gather
+        self.torch = torch
+        self.stages = WORKLOADS[name]
+        self.world = ctx["world"]
+        shape_world = self.world
+        if shard_of > 1:
+            if self.world != 1 or any(len(st) > 5 for st in self.stages):
+                raise SystemExit("bench.py --shard-of needs a single process and a workload without a gather")
+            shape_world = shard_of
+        self.shape_world = shape_world
+        dev = ctx["dev"]
+        self.host = [gen_stage(st, ctx["rank"], shape_world, 2024 + i, dev, host_x=host_x)
+                     for i, st in enumerate(self.stages)]
+        self.gpu = self.build_set()
+        torch.cuda.synchronize()
+        self.resident = sum(s["bytes_resident"] for s in self.gpu)
+        # Small workloads would run from L2 if the same buffers were reused every step: rotate over
+        # enough independent copies of the per-step buffers AND weights that a copy's lines have been
+        # evicted (more than 2.5 x L2 of other traffic) before it is used again.  No flush kernel is
+        # needed and the steps stay back to back.
+        self.rot = [self.gpu]
+        if self.resident < 2 * ctx["l2_bytes"]:
+            copies = int(math.ceil(2.5 * ctx["l2_bytes"] / max(self.resident, 1))) + 1
+            for c in range(copies - 1):
+                self.rot.append(self.build_set(fresh_weights=True))
+            torch.cuda.synchronize()
+        self.flops_rank = sum(s["flops"] for s in self.gpu)
+        self.flops_total = self.flops_rank * self.world
+        self.turn = 0
+
+    def build_set(self, share_from=None, fresh_weights=False):
+        """One set of per-step buffers + plans for all stages.  When a stage feeds a chained
+        consumer on several GPUs, its output goes to a symmetric gathered buffer: fused into the
+        producer's epilogue (gather == "fused") or by ncclAllGather afterwards ("nccl")."""
+        ctx, torch = self.ctx, self.torch
+        xf, capi, dist, dev = ctx["xf"], ctx["capi"], ctx["dist"], ctx["dev"]
+        out, pending = [], None
+        for i, (st, h) in enumerate(zip(self.stages, self.host)):
+            if fresh_weights:      # an independent copy of every operand of the stage
+                h = {k: (v.clone() if hasattr(v, "clone") and v is not None and v.device == dev else v)
+                     for k, v in h.items()}
+            nxt_chain = i + 1 < len(self.stages) and len(self.stages[i + 1]) > 5
+            gather = None
+            if nxt_chain and self.world > 1 and self.gather == "fused":
+                n_out = (st[2] // self.world) // (2 if st[0] == "k2" else 1)
+                gather = xf.sharding.GatherBuffer(dist, st[1], n_out, torch.bfloat16, dev)
+            out.append(build_stage_gpu(capi, st, h, dev, share=share_from[i] if share_from else None,
+                                       prev=out[-1] if out else None, world=self.world, gather=gather,
+                                       consume=pending))
+            pending = gather
+        return out
+
+    def run_stages(self, stage_list, stream=None):
+        xf, dist = self.ctx["xf"], self.ctx["dist"]
+        for s in stage_list:
+            if "gather_from" in s:   # the one exchange of the path: output shards -> K slabs
+                xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
+            if "barrier" in s:       # slabs were written by the producers' epilogues: wait for all
+                s["barrier"].barrier()
+            s["plan"].run(stream)
+
+    def step(self):
+        self.run_stages(self.rot[self.turn % len(self.rot)])
+        self.turn += 1
+
+    def max_over_ranks(self, ms):
+        dist = self.ctx["dist"]
+        if dist is None:
+            return ms
+        t = self.torch.tensor([ms], device=self.ctx["dev"])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def check_status(self):
+        for g in self.rot:
+            for s in g:
+                if s["plan"].device_status() != 0:
+                    raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
+
+    def timed(self, steps, warmup):
+        """(TFLOP/s whole job, ms per step): EXACTLY `steps` steps between two barriers."""
+        barrier = self.ctx["barrier"]
+        for _ in range(warmup):
+            self.step()
+        barrier()
+        ms = time_loop(self.torch, self.step, steps)
+        barrier()
+        ms = self.max_over_ranks(ms)
+        self.check_status()
+        return self.flops_total * steps / (ms * 1e-3) / 1e12, ms / steps
+
+    def sustained(self, ms_per_step, seconds=0.5, min_steps=0):
+        """The same step back to back for about `seconds`: (TFLOP/s, ms per step, wall window)."""
+        barrier = self.ctx["barrier"]
+        n = max(min_steps, min(20000, int(seconds / max(ms_per_step * 1e-3, 1e-6))))
+        barrier()
+        t0 = time.time()
+        ms = time_loop(self.torch, self.step, n)
+        t1 = time.time()
+        barrier()
+        ms = self.max_over_ranks(ms)
+        return self.flops_total * n / (ms * 1e-3) / 1e12, ms / n, (t0 + 0.1, t1), n
+
+    def kernels(self):
+        return [s["plan"].kernel_name for s in self.gpu]
+
+    # ---- end to end through the C ABI with host buffers: every step copies its activations and
+    # row scales from pinned host memory and reads its whole output back.  Two device buffer sets
+    # and three streams (copy-in, compute, copy-out) let step i+1's upload and step i-1's read-back
+    # overlap step i's kernels, as a serving loop would; weights stay resident.
+    def e2e(self, steps):
+        torch, ctx = self.torch, self.ctx
+        dev, dist, world, rank = ctx["dev"], ctx["dist"], self.world, ctx["rank"]
+        gpu = self.gpu
+        gpu2 = self.build_set(share_from=gpu)
+        sets = [gpu, gpu2]
+        outs = [[torch.empty(s["D"].shape, dtype=torch.bfloat16).pin_memory() for s in gpu] for _ in range(2)]
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        s_comp = torch.cuda.current_stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_k = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
+        # From 4 ranks up the replicated activations are uploaded in row shards and exchanged over
+        # NVLink: at 2 ranks the read-back of the output is the longer PCIe transfer either way and
+        # the gather kernel only takes SMs from the persistent GEMM.
+        shard_upload = world >= 4 and all(s["chain"] or s["X"].shape[0] % world == 0 for s in gpu)
+        host = self.host
+
+        def loop(n):
+            for i in range(n):
+                b = i & 1
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_k[b])            # the kernels that read this buffer set are done
+                    for s, h in zip(sets[b], host):
+                        if not s["chain"]:
+                            if shard_upload:
+                                m = s["X"].shape[0] // world
+                                mine = s["X"][rank * m:(rank + 1) * m]
+                                mine.copy_(h["X"][rank * m:(rank + 1) * m], non_blocking=True)
+                                dist.all_gather_into_tensor(s["X"], mine)
+                            else:
+                                s["X"].copy_(h["X"], non_blocking=True)
+                            s["R"].copy_(h["R"], non_blocking=True)
+                    ev_in[b].record(s_in)
+                s_comp.wait_event(ev_in[b])
+                s_comp.wait_event(ev_out[b])            # the previous read-back of this output is done
+                self.run_stages(sets[b], s_comp.cuda_stream)
+                ev_k[b].record(s_comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_k[b])
+                    for s, o in zip(sets[b], outs[b]):
+                        o.copy_(s["D"], non_blocking=True)
+                    ev_out[b].record(s_out)
+            s_comp.wait_stream(s_in)
+            s_comp.wait_stream(s_out)
+
+        loop(4)
+        ctx["barrier"]()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s_comp)
+        loop(steps)
+        e1.record(s_comp)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        ctx["barrier"]()
+        ms = self.max_over_ranks(ms)
+        h2d_job = d2h_job = 0          # bytes that cross PCIe per step, all ranks together
+        for s in gpu:
+            d2h_job += s["d2h_bytes"] * world
+            if not s["chain"]:
+                x_bytes = s["X"].numel() * s["X"].element_size()
+                h2d_job += (x_bytes if shard_upload else x_bytes * world) + (s["h2d_bytes"] - x_bytes) * world
+        return {"value": self.flops_total * steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(h2d_job), "d2h_bytes_per_step": int(d2h_job),
+                "ms_per_step": ms / steps,
+                "how": "double-buffered: H2D of step i+1 and D2H of step i-1 overlap the kernels of step i; "
+                       "bytes are whole-job totals over all ranks"
+                       + ("; each rank uploads 1/N of the replicated activation rows and the ranks "
+                          "all-gather them over NVLink" if shard_upload else "")}
+
+    # ---- unfused baseline: bare GEMM + stand-alone kernel(s)
+    def unfused(self, steps, fused_value):
+        ctx = self.ctx
+        xf, capi, dist, dev = ctx["xf"], ctx["capi"], ctx["dist"], ctx["dev"]
+        us_rot = [[build_unfused(capi, s, dev) for s in g] for g in self.rot]
+
+        def ustep():
+            k = self.turn % len(self.rot)
+            self.turn += 1
+            for u, s in zip(us_rot[k], self.rot[k]):
+                if "gather_from" in s:   # same exchange as the fused arm
+                    xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
+                if "barrier" in s:       # unfused arm: gather the fused producer's slab with NCCL
+                    xf.sharding.all_gather_shards(dist, s["barrier"].local_shard, s["X"])
+                u["plan"].run()
+                u["post"]()
+
+        for _ in range(3):
+            ustep()
+        ctx["barrier"]()
+        ms = time_loop(self.torch, ustep, steps)
+        ctx["barrier"]()
+        ms = self.max_over_ranks(ms)
+        v = self.flops_total * steps / (ms * 1e-3) / 1e12
+        return {"value": v, "unit": "TFLOP/s", "ms_per_step": ms / steps, "fused_speedup": fused_value / v,
+                "launches_per_step": sum(u["launches"] for u in us_rot[0])}
+
+    def l2_note(self):
+        l2 = self.ctx["l2_bytes"]
+        if len(self.rot) > 1:
+            return (f"steps rotate over {len(self.rot)} independent copies of the working set "
+                    f"({(self.resident * len(self.rot)) >> 20} MiB in all > 2.5 x L2 {l2 >> 20} MiB), no flush")
+        return f"resident inputs+outputs {self.resident >> 20} MiB > L2 {l2 >> 20} MiB, no flush"
+
+
+def measure_int8_peak(ctx):
+    """int8 tensor-core rate of this GPU on an 8192^3 problem in local memory: cuBLASLt through
+    torch._int_mm (the library yardstick) and this library's bare int8 kernel (int32 output, no
+    epilogue).  Best of 10 single launches, CUDA events.  TOP/s."""
+    torch, capi, dev = ctx["torch"], ctx["capi"], ctx["dev"]
+    n = 8192
+    out = {"shape": "8192^3 int8 -> int32", "how": "best of 10 single launches, CUDA events"}
+    A = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev)
+    B = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev)
+
+    def best(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        t = []
+        for _ in range(10):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            t.append(a.elapsed_time(b))
+        return 2.0 * n ** 3 / (min(t) * 1e-3) / 1e12
+
+    try:
+        Bt = B.t().contiguous().t()        # column-major B: the layout cuBLASLt's int8 GEMM wants
+        out["torch_int_mm"] = best(lambda: torch._int_mm(A, Bt))
+    except Exception as e:                 # noqa: BLE001  (library call that may refuse the layout)
+        out["torch_int_mm"] = None
+        out["torch_int_mm_error"] = str(e)[:120]
+    D = torch.empty((n, n), dtype=torch.int32, device=dev)
+    plan = capi.GemmPlan(A, B, D)
+    out["own_bare_kernel"] = best(plan.run)
+    out["kernel"] = plan.kernel_name
+    return out
+
+
+def gather_check(ctx, steps=2):
+    """N > 1: the all-gather fused into the producer's epilogue against ncclAllGather, bit for bit,
+    on a small gate/up -> down chain: the gathered buffers must be identical and so must the
+    consumer's outputs.  Returns "pass" or a short failure text."""
+    torch, dist, dev, xf, capi = ctx["torch"], ctx["dist"], ctx["dev"], ctx["xf"], ctx["capi"]
+    world, rank = ctx["world"], ctx["rank"]
+    sh = xf.sharding
+    M, K1, N2 = 512, 512, 512
+    N1 = 2 * 256 * 2 * world
+    g = torch.Generator(device=dev).manual_seed(5)            # identical on every rank: replicated inputs
+    X = torch.randn(M, K1, generator=g, device=dev).to(torch.bfloat16)
+    R = torch.rsqrt((X.float() ** 2).mean(dim=1) + 1e-6).contiguous()
+    W1 = (torch.randn(K1, N1, generator=g, device=dev) * K1 ** -0.5).to(torch.bfloat16)
+    W2 = (torch.randn(N1 // 2, N2, generator=g, device=dev) * (N1 // 2) ** -0.5).to(torch.bfloat16)
+    lo, hi = sh.shard_columns(N1, world, rank, sh.stage_multiple("k2", compact=True))
+    ns = (hi - lo) // 2
+    W1s = W1[:, lo:hi].contiguous()
+    gb = sh.GatherBuffer(dist, M, ns, torch.bfloat16, dev)
+    gb.tensor.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    prod = capi.GemmPlan(X, W1s, gb.local_shard, row_scale=R, pair="swiglu", compact=True,
+                         d_peer_ptrs=gb.peer_slab_ptrs())
+    out_f = torch.empty(M, N2, dtype=torch.bfloat16, device=dev)
+    cons_f = capi.GemmPlan(gb.tensor, W2, out_f, a_k_slabs=True)
+    shard = torch.empty(M, ns, dtype=torch.bfloat16, device=dev)
+    gathered = torch.zeros(world, M, ns, dtype=torch.bfloat16, device=dev)
+    prod_n = capi.GemmPlan(X, W1s, shard, row_scale=R, pair="swiglu", compact=True)
+    out_n = torch.empty(M, N2, dtype=torch.bfloat16, device=dev)
+    cons_n = capi.GemmPlan(gathered, W2, out_n, a_k_slabs=True)
+    for _ in range(steps):
+        prod.run()
+        gb.barrier()
+        cons_f.run()
+        prod_n.run()
+        sh.all_gather_shards(dist, shard, gathered)
+        cons_n.run()
+        gb.barrier()              # nobody overwrites a slab a peer may still read
+    torch.cuda.synchronize()
+    ok = torch.equal(gb.tensor.view(torch.int16), gathered.view(torch.int16)) and \
+        torch.equal(out_f.view(torch.int16), out_n.view(torch.int16)) and bool(out_f.float().abs().sum() > 0)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return "pass" if int(flag.item()) == 1 else "FAIL: fused gather differs from ncclAllGather on some rank"
 
 
 # ------------------------------------------------------------------------------ CPU arm
+def cpu_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_sample(stages, seconds_target, seed):
     """Times the oracle on a row-sample of the workload; returns (tflops, rows, seconds, cores)."""
+    # all the host cores this process may use, whatever the launcher put in OMP_NUM_THREADS
+    # (torch.distributed.run sets it to 1)
+    os.environ["OMP_NUM_THREADS"] = str(cpu_threads())
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import numpy as np
     import oracle as o
     o.build()
+    o.set_num_threads(cpu_threads())
     rng = np.random.default_rng(seed)
     cores = o.num_threads()
     # bound the sample by columns too so that the widened weight panel stays small
@@ -328,7 +654,7 @@ def cpu_sample(stages, seconds_target, seed):
     for (preset, M, N, K, dt) in [st[:5] for st in stages]:
         Nc = min(N, 4096)
         plans.append((preset, M, Nc, K, dt))
-    # calibrate on 16 rows
+
     def run(rows):
         t = 0.0
         fl = 0.0
@@ -368,7 +694,8 @@ def cpu_sample(stages, seconds_target, seed):
 
 def run_reference_arm(args, stages):
     """`--impl reference`: the reference's path on the host cores.  The reference itself is SYCL
-    for Intel Xe with no host implementation, so this is the CPU oracle (a port of its formulas)."""
+    for Intel Xe with no host implementation, so this is the CPU oracle (a port of its formulas),
+    on every core this process may use.  Under torch.distributed.run only rank 0 works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -414,6 +741,9 @@ def main():
                          "(the kernel a rank of --gpus N launches), e.g. to profile it; not a job figure")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-unfused", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip all_configs (1 GPU) / pipeline + gather check (N > 1) and the int8 peak")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -445,71 +775,17 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    peaks = load_peaks()
-    l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
-
-    shape_world = world
-    if args.shard_of > 1:
-        if world != 1 or any(len(st) > 5 and st[5] == "chain" for st in stages):
-            raise SystemExit("bench.py --shard-of needs a single process and a workload without a gather")
-        shape_world = args.shard_of
-    host = [gen_stage_host(st, rank, shape_world, seed=2024 + i) for i, st in enumerate(stages)]
-
-    def build_set(share_from=None):
-        """One set of per-step buffers + plans for all stages.  When a stage feeds a chained
-        consumer on several GPUs, its output goes to a symmetric gathered buffer: fused into the
-        producer's epilogue (--gather fused) or by ncclAllGather afterwards (--gather nccl)."""
-        out, pending = [], None
-        for i, (st, h) in enumerate(zip(stages, host)):
-            nxt_chain = i + 1 < len(stages) and len(stages[i + 1]) > 5
-            gather = None
-            if nxt_chain and world > 1 and args.gather == "fused":
-                n_out = (st[2] // world) // (2 if st[0] == "k2" else 1)
-                gather = xf.sharding.GatherBuffer(dist, st[1], n_out, torch.bfloat16, dev)
-            out.append(build_stage_gpu(capi, st, h, dev, share=share_from[i] if share_from else None,
-                                       prev=out[-1] if out else None, world=world, gather=gather, consume=pending))
-            pending = gather
-        return out
-
-    gpu = build_set()
-    torch.cuda.synchronize()
-    resident = sum(s["bytes_resident"] for s in gpu)
-    # Small workloads would run from L2 if the same buffers were reused every step: rotate over
-    # enough independent copies of the whole working set that a copy's lines have been evicted
-    # (more than 2.5 x L2 of other traffic) before it is used again.  No flush kernel is needed and
-    # the steps stay back to back.
-    flush = None
-    rot = [gpu]
-    if resident < 2 * l2_bytes:
-        copies = int(math.ceil(2.5 * l2_bytes / max(resident, 1))) + 1
-        rot += [build_set() for _ in range(copies - 1)]
-        torch.cuda.synchronize()
-    flops_rank = sum(s["flops"] for s in gpu)
-    flops_total = flops_rank * world
-
-    def run_stages(stage_list, stream=None):
-        for s in stage_list:
-            if "gather_from" in s:   # the one exchange of the path: output shards -> K slabs
-                xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
-            if "barrier" in s:       # slabs were written by the producers' epilogues: wait for all
-                s["barrier"].barrier()
-            s["plan"].run(stream)
-
-    turn = [0]
-
-    def step():
-        run_stages(rot[turn[0] % len(rot)])
-        turn[0] += 1
-
     def barrier():
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
+    peaks = load_peaks()
+    ctx = {"torch": torch, "xf": xf, "capi": capi, "dist": dist, "dev": dev, "world": world, "rank": rank,
+           "barrier": barrier, "l2_bytes": torch.cuda.get_device_properties(dev).L2_cache_size}
+
+    wl = Workload(ctx, args.workload, gather=args.gather, shard_of=args.shard_of)
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     if not uuid.startswith("GPU-"):
         uuid = "GPU-" + uuid
@@ -517,159 +793,81 @@ def main():
     sampler.start()
     time.sleep(0.15)
     # EXACTLY `steps` steps are timed.  That region is milliseconds long, shorter than one
-    # nvidia-smi sample, so the same step is then repeated untimed for about half a second and the
-    # SM clock is read over that window; throttle reasons are collected over the whole run.
-    t0w = time.time()
-    ms = time_loop(torch, step, args.steps, flush)
-    barrier()
-    t1w = time.time()
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    for g in rot:
-        for s in g:
-            if s["plan"].device_status() != 0:
-                raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
-    value = flops_total * args.steps / (ms * 1e-3) / 1e12
-    ms_per_step = ms / args.steps
-    # the same number of repeats on every rank (ms is the max over ranks): stages may hold collectives
-    load_steps = max(args.steps, min(20000, int(0.5 / max(ms_per_step * 1e-3, 1e-6))))
-    tl0 = time.time()
-    for i in range(load_steps):
-        step()
-        if i % 64 == 63:
-            torch.cuda.synchronize()
-    barrier()
-    tl1 = time.time()
+    # nvidia-smi sample, so the same step is then repeated for about half a second, timed as
+    # value_sustained, and the SM clock is read over that window; throttle reasons are collected
+    # over the whole run.
+    value, ms_per_step = wl.timed(args.steps, args.warmup)
+    v_sus, ms_sus, load_window, n_sus = wl.sustained(ms_per_step, min_steps=args.steps)
+    sm_sus, _ = sampler.median_sm(*load_window)
 
-    # ---- end to end through the C ABI with host buffers: every step copies its activations and
-    # row scales from pinned host memory and reads its whole output back.  Two device buffer sets
-    # and three streams (copy-in, compute, copy-out) let step i+1's upload and step i-1's read-back
-    # overlap step i's kernels, as a serving loop would; weights stay resident.
-    gpu2 = build_set(share_from=gpu)
-    sets = [gpu, gpu2]
-    outs = [[torch.empty(s["D"].shape, dtype=torch.bfloat16).pin_memory() for s in gpu] for _ in range(2)]
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    s_comp = torch.cuda.current_stream()
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_k = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+    e2e = None if args.no_e2e else wl.e2e(args.steps)
+    unfused = None if args.no_unfused else wl.unfused(args.steps, value)
+    is_s8 = stages[0][4] == "s8"
+    kernels = wl.kernels()
+    l2_note = wl.l2_note()
+    flops_rank, shape_world = wl.flops_rank, wl.shape_world
+    n_stage = len(wl.gpu)
+    has_chain = any(s["chain"] for s in wl.gpu)
+    del wl
+    torch.cuda.empty_cache()
 
-    # From 4 ranks up the replicated activations are uploaded in row shards and exchanged over
-    # NVLink: at 2 ranks the read-back of the output is the longer PCIe transfer either way and the
-    # gather kernel only takes SMs from the persistent GEMM (measured: 813 vs 713 TFLOP/s).
-    shard_upload = world >= 4 and all(s["chain"] or s["X"].shape[0] % world == 0 for s in gpu)
+    # ---- extras: the other configurations (1 GPU) or the collective-bearing chain (N > 1)
+    default_run = args.workload == "k2" and args.shard_of <= 1 and not args.no_extras
+    int8_peak = None
+    if (is_s8 or (default_run and world == 1)) and not args.no_extras:
+        int8_peak = measure_int8_peak(ctx)
+    int8_den = (int8_peak or {}).get("torch_int_mm") or 2.0 * peaks["bf16"]
 
-    def e2e_loop(n):
-        for i in range(n):
-            b = i & 1
-            with torch.cuda.stream(s_in):
-                s_in.wait_event(ev_k[b])            # the kernels that read this buffer set are done
-                for s, h in zip(sets[b], host):
-                    if not s["chain"]:
-                        if shard_upload:
-                            # replicated activations: each rank uploads 1/world of the rows over its
-                            # own PCIe link and the ranks exchange them over NVLink (in-place gather)
-                            m = s["X"].shape[0] // world
-                            mine = s["X"][rank * m:(rank + 1) * m]
-                            mine.copy_(h["X"][rank * m:(rank + 1) * m], non_blocking=True)
-                            dist.all_gather_into_tensor(s["X"], mine)
-                        else:
-                            s["X"].copy_(h["X"], non_blocking=True)
-                        s["R"].copy_(h["R"], non_blocking=True)
-                ev_in[b].record(s_in)
-            s_comp.wait_event(ev_in[b])
-            s_comp.wait_event(ev_out[b])            # the previous read-back of this output is done
-            run_stages(sets[b], s_comp.cuda_stream)
-            ev_k[b].record(s_comp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_k[b])
-                for s, o in zip(sets[b], outs[b]):
-                    o.copy_(s["D"], non_blocking=True)
-                ev_out[b].record(s_out)
-        s_comp.wait_stream(s_in)
-        s_comp.wait_stream(s_out)
+    def frac_of_peak(tflops_per_gpu, s8):
+        return tflops_per_gpu / (int8_den if s8 else peaks["bf16"])
 
-    e2e_loop(4)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(s_comp)
-    e2e_loop(args.steps)
-    e1.record(s_comp)
-    torch.cuda.synchronize()
-    ms_e2e = e0.elapsed_time(e1)
-    barrier()
-    if dist is not None:
-        t = torch.tensor([ms_e2e], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item())
-    # bytes that cross PCIe per step, all ranks together
-    h2d_job = d2h_job = 0
-    for s in gpu:
-        d2h_job += s["d2h_bytes"] * world                       # every rank reads its own shard back
-        if not s["chain"]:
-            x_bytes = s["X"].numel() * s["X"].element_size()
-            h2d_job += (x_bytes if shard_upload else x_bytes * world) + (s["h2d_bytes"] - x_bytes) * world
-    e2e = {"value": flops_total * args.steps / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
-           "h2d_bytes_per_step": int(h2d_job), "d2h_bytes_per_step": int(d2h_job),
-           "ms_per_step": ms_e2e / args.steps,
-           "how": "double-buffered: H2D of step i+1 and D2H of step i-1 overlap the kernels of step i; "
-                  "bytes are whole-job totals over all ranks"
-                  + ("; each rank uploads 1/N of the replicated activation rows and the ranks "
-                     "all-gather them over NVLink" if shard_upload else "")}
-    del gpu2, sets
-
-    # ---- unfused baseline: bare GEMM + stand-alone kernel(s)
-    unfused = None
-    if not args.no_unfused:
-        us_rot = [[build_unfused(capi, s, dev) for s in g] for g in rot]
-        us = us_rot[0]
-
-        def unfused_step():
-            k = turn[0] % len(rot)
-            turn[0] += 1
-            for u, s in zip(us_rot[k], rot[k]):
-                if "gather_from" in s:   # same exchange as the fused arm
-                    xf.sharding.all_gather_shards(dist, s["gather_from"], s["X"])
-                if "barrier" in s:       # unfused arm: gather the fused producer's slab with NCCL
-                    xf.sharding.all_gather_shards(dist, s["barrier"].local_shard, s["X"])
-                u["plan"].run()
-                u["post"]()
-
-        for _ in range(3):
-            unfused_step()
-        barrier()
-        ms_u = time_loop(torch, unfused_step, args.steps, flush)
-        barrier()
-        if dist is not None:
-            t = torch.tensor([ms_u], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_u = float(t.item())
-        v_u = flops_total * args.steps / (ms_u * 1e-3) / 1e12
-        unfused = {"value": v_u, "unit": "TFLOP/s", "ms_per_step": ms_u / args.steps,
-                   "fused_speedup": value / v_u, "launches_per_step": sum(u["launches"] for u in us)}
-        del us, us_rot
-    clocks = sampler.stop(t0w, time.time(), load_window=(tl0 + 0.1, tl1))
+    all_configs = None
+    if default_run and world == 1:
+        all_configs = {}
+        for name in OTHER_CONFIGS:
+            w = Workload(ctx, name, host_x=False)
+            steps = 20
+            v, ms = w.timed(steps, 3)
+            u = w.unfused(steps, v)
+            s8 = WORKLOADS[name][0][4] == "s8"
+            all_configs[name] = {"value": v, "unit": "TOP/s" if s8 else "TFLOP/s", "ms_per_step": ms,
+                                 "frac": frac_of_peak(v, s8), "unfused": u["value"],
+                                 "fused_speedup": u["fused_speedup"], "kernels": w.kernels(), "steps": steps}
+            del w, u
+            torch.cuda.empty_cache()
+    pipeline = None
+    if default_run and world > 1:
+        pipeline = {"workload": DESCR["pipeline"], "gather_check": gather_check(ctx)}
+        for mode in ("fused", "nccl"):
+            w = Workload(ctx, "pipeline", gather=mode, host_x=False)
+            v, ms = w.timed(10, 3)
+            gathered_bytes = 8192 * (57344 // 2) * 2             # the gate/up output, bf16
+            pipeline[mode] = {"value": v, "unit": "TFLOP/s", "ms_per_step": ms,
+                              "frac_per_gpu": frac_of_peak(v / world, False), "kernels": w.kernels(),
+                              "nvlink_bytes_out_per_rank_per_step": gathered_bytes // world * (world - 1)}
+            del w
+            torch.cuda.empty_cache()
+    clocks = sampler.stop(load_window=load_window)
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    is_s8 = stages[0][4] == "s8"
-    peak = peaks["bf16"] * (2.0 if is_s8 else 1.0)
+    peak = int8_den if is_s8 else peaks["bf16"]
     achieved = flops_rank / (ms_per_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": None,
-                "peak_source": ("2 x measured bf16 burst (int8 runs at twice the bf16 rate; no int8 peak was measured)"
+                "peak_source": ((f"int8 rate of torch._int_mm (cuBLASLt) at 8192^3 measured in this run; "
+                                 f"this library's bare int8 kernel on the same problem: "
+                                 f"{(int8_peak or {}).get('own_bare_kernel')}"
+                                 if (int8_peak or {}).get("torch_int_mm") else
+                                 "2 x measured bf16 burst (no int8 library GEMM could be timed)")
                                 if is_s8 else f"bf16 burst, {peaks['src']}"),
-                "frac_of_sustained": achieved / (peaks["bf16_sustained"] * (2.0 if is_s8 else 1.0))
-                if peaks.get("bf16_sustained") else None,
                 "frac_of_nominal": achieved / (4500.0 if is_s8 else 2250.0),
-                "kernel": ",".join(sorted({s["plan"].kernel_name for s in gpu}))}
-    if world == 1:
-        roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
+                "kernel": ",".join(sorted(set(kernels)))}
+    if world == 1 and args.shard_of <= 1:
+        roofline["traffic"] = load_traffic().get(args.workload)
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
@@ -677,6 +875,13 @@ def main():
         cpu_baseline = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                         "sample": f"{rows} rows x {cols} columns x full K of the workload, {t:.1f} s of CPU time"}
 
+    sus_den = peaks.get("bf16_sustained")
+    value_sustained = {
+        "value": v_sus, "unit": "TFLOP/s", "ms_per_step": ms_sus, "steps": n_sus, "sm_mhz_median": sm_sus,
+        "ms_x_mhz": (ms_sus * sm_sus) if sm_sus else None,
+        "frac_of_sustained_peak": (v_sus / world / (sus_den * (2.0 if is_s8 else 1.0))) if sus_den else None,
+        "how": "the timed step back to back for ~0.5 s (power-capped clocks); fraction of the measured "
+               "bf16_tflops_sustained (x2 for int8); ms_x_mhz lets runs at different clocks be compared"}
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -687,15 +892,18 @@ def main():
                                 f"weight columns N split {shape_world}-way, activations and row scales replicated, no collective inside a stage"
                                 + ((f"; gate/up output shards all-gathered into K slabs for the down projection "
                                     f"({'peer stores from the epilogue' if args.gather == 'fused' else 'ncclAllGather'})")
-                                   if world > 1 and any(s["chain"] for s in gpu) else "")),
-                   "l2": (f"steps rotate over {len(rot)} independent copies of the working set "
-                          f"({(resident * len(rot)) >> 20} MiB in all > 2.5 x L2 {l2_bytes >> 20} MiB), no flush"
-                          if len(rot) > 1 else
-                          f"resident inputs+outputs {resident >> 20} MiB > L2 {l2_bytes >> 20} MiB, no flush"),
-                   "kernels": [s["plan"].kernel_name for s in gpu]},
+                                   if world > 1 and has_chain else "")),
+                   "l2": l2_note, "kernels": kernels},
+        "value_sustained": value_sustained,
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "unfused": unfused,
-        "gpu_launches": args.steps * len(gpu), "clocks": clocks,
+        "gpu_launches": args.steps * n_stage, "clocks": clocks,
     }
+    if int8_peak is not None:
+        line["int8_peak"] = int8_peak
+    if all_configs is not None:
+        line["all_configs"] = all_configs
+    if pipeline is not None:
+        line["pipeline"] = pipeline
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

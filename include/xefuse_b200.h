@@ -183,9 +183,6 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_FORCE_KS1    32  /* one 128-byte K slab per pipeline stage */
 #define XF_FLAG_FORCE_KS2    64  /* two 128-byte K slabs per pipeline stage */
 #define XF_FLAG_NO_SPLIT     128 /* never cut the tiles of the last, partly filled wave into K slices */
-#define XF_FLAG_DIAG_NO_LOAD  256 /* timing diagnostics only: skip the TMA operand loads (D is garbage) */
-#define XF_FLAG_DIAG_NO_MMA   512 /* timing diagnostics only: skip the tensor-core MMAs (D is garbage) */
-#define XF_FLAG_DIAG_NO_EPILOGUE 1024 /* timing diagnostics only: drain TMEM, compute and store nothing */
 #define XF_FLAG_SHORT_WAITS 8192 /* bounded waits inside the kernel give up after about a millisecond
                                     instead of about two seconds (fail fast; also how the give-up
                                     path is tested) */
@@ -195,6 +192,20 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_NO_PDL      4096 /* launch without programmatic stream serialization: by default the
                                     kernel's set-up may overlap the tail of the previous kernel of the
                                     stream; its global reads and writes always wait for that kernel */
+#define XF_FLAG_NO_CLUSTER_SPLIT 65536 /* never use the cluster split-K variants (small problems: the CTA
+                                    pairs of one cluster share a tile's K range and swap partial
+                                    accumulators through distributed shared memory) */
+#define XF_FLAG_FORCE_CLUSTER_SPLIT 131072 /* use a cluster split-K variant whenever K is long enough, also
+                                    for problems with more tiles than co-resident clusters */
+
+/* Timing diagnostics, not for production: each flag removes one part of the kernel and leaves D
+ * GARBAGE.  They are refused (XF_ERR_NOT_SUPPORTED) unless the environment holds
+ * XEFUSE_ALLOW_DIAG=1 when the problem is checked. */
+#define XF_FLAG_DIAG_NO_LOAD  256    /* skip the TMA operand loads */
+#define XF_FLAG_DIAG_NO_MMA   512    /* skip the tensor-core MMAs */
+#define XF_FLAG_DIAG_NO_EPILOGUE 1024 /* drain TMEM, compute and store nothing */
+#define XF_FLAG_DIAG_NO_STORE 2048   /* run the epilogue math, store nothing */
+#define XF_FLAG_DIAG_MASK (256 | 512 | 1024 | 2048)
 
 typedef struct xf_plan xf_plan;
 
@@ -208,13 +219,20 @@ XF_API xf_status xf_gemm_workspace_size(const xf_gemm_desc* desc, size_t* bytes)
 /* Copies the descriptor, picks a kernel, encodes TMA tensor maps.  workspace may be NULL when
  * xf_gemm_workspace_size reported 0; otherwise it must stay valid for the plan's lifetime. */
 XF_API xf_status xf_gemm_plan_create(const xf_gemm_desc* desc, void* workspace, xf_plan** plan);
-/* Enqueues one fused launch on `stream` (a cudaStream_t; NULL = default stream).  Re-entrant. */
+/* Enqueues one fused launch on `stream` (a cudaStream_t; NULL = default stream).  Re-entrant.  The
+ * device the plan was created on must be current (XF_ERR_INVALID_PROBLEM otherwise). */
 XF_API xf_status xf_gemm_run(xf_plan* plan, void* stream);
-/* Reads back (synchronously) the device status word of the plan's last launches:
+/* How many CTA pairs and how many 4-CTA clusters (cluster split-K, two pairs per tile) of the
+ * 256 x 256 kernel the current device can hold at once for the given input type: the scheduling
+ * units the planner counts in (74 and about 36 on a 148-SM B200; GPC boundaries decide). */
+XF_API xf_status xf_gemm_cluster_capacity(int32_t dtype_ab, int32_t* pairs, int32_t* quads);
+/* Reads back the device status word of the plan's last launches.  Synchronise the stream(s) the
+ * plan ran on first: the read itself only orders against the legacy default stream.
  * 0 = ok (returns XF_SUCCESS), otherwise the code of the bounded wait that gave up: 1 producer
  * waiting for a free stage, 2 MMA issuer waiting for operands, 3 MMA issuer waiting for a free
  * accumulator, 4 epilogue waiting for the accumulator, 5 a K slice waiting for the other slices'
- * partials (returns XF_ERR_INTERNAL; the outputs of that launch are not valid).  A non-zero code is
+ * partials, 6 a cluster split-K pair waiting for the other pairs' partials (returns XF_ERR_INTERNAL;
+ * the outputs of that launch are not valid).  A non-zero code is
  * reported once: the word and the split counters are cleared so the plan can run again. */
 XF_API xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code);
 /* Name of the kernel variant the plan selected, e.g. "bf16_128x256_cta2_s6". */
@@ -229,20 +247,28 @@ XF_API xf_status xf_plan_destroy(xf_plan* plan);
  * whose callers always allocate a workspace (tests/test_k1.cpp:96-97).
  *
  * The caller passes inputs and outputs in `desc` as usual.  The kernel's scratch -- the status
- * word of its bounded waits -- lives in a static device array of XF_STATIC_WORKSPACE_BYTES that
- * each GPU using the library holds until process exit; a problem whose workspace requirement
- * (xf_gemm_workspace_size) exceeds that is refused with XF_ERR_NOT_SUPPORTED.  No cudaMalloc,
- * cudaFree or host allocation happens inside: the plan lives on the stack and is rebuilt on every
- * call (three tensor-map encodes), so prefer a plan when you can allocate.
+ * word of its bounded waits and, when the tiles of the last wave are cut into K slices, the slice
+ * counters and partial accumulators -- lives in a static device array of
+ * XF_STATIC_WORKSPACE_BYTES (2 MiB) that each GPU using the library holds until process exit.  A
+ * problem whose schedule needs more than that (xf_gemm_workspace_size tells) is refused with
+ * XF_ERR_NOT_SUPPORTED and a message naming the size; pass XF_FLAG_NO_SPLIT to run it with whole
+ * tiles, which needs 16 bytes.  No cudaMalloc, cudaFree or host allocation happens inside: the
+ * plan lives on the stack and is rebuilt on every call (three tensor-map encodes), so prefer a
+ * plan when you can allocate.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current); make that first call outside any stream capture.  All calls on a device
- * share the array and each call clears the words it uses on `stream` before its kernel, so calls
- * whose kernels may overlap on the GPU (different streams, no ordering between them) race on it:
- * order them, or use plans with separate workspaces.
+ * share the array and each call clears the words it needs at zero on `stream` before its kernel,
+ * so calls whose kernels may overlap on the GPU (different streams, no ordering between them)
+ * race on it: order them, or use plans with separate workspaces.
  */
-#define XF_STATIC_WORKSPACE_BYTES 256
+#define XF_STATIC_WORKSPACE_BYTES 2097152
 XF_API xf_status xf_gemm_run_static_workspace(const xf_gemm_desc* desc, void* stream);
+/* Status word of the static array on the current device, with the contract of
+ * xf_gemm_plan_device_status: 0 = the launches since the last query were fine; otherwise the code
+ * of the bounded wait that gave up (XF_ERR_INTERNAL; reported once, then cleared).  Synchronise
+ * the stream(s) first.  Allocates nothing.  No counterpart in the reference either. */
+XF_API xf_status xf_gemm_static_workspace_status(int32_t* device_code);
 
 /* Thread-local text of the last error produced by any entry point on this thread. */
 XF_API const char* xf_last_error_string(void);

@@ -52,6 +52,14 @@ XO_API void xo_bf16_to_f32(const uint16_t* src, float* dst, int64_t n) {
   for (int64_t i = 0; i < n; ++i) dst[i] = bf16_to_f32(src[i]);
 }
 
+XO_API void xo_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 XO_API int xo_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

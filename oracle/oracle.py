@@ -5,13 +5,32 @@ library never does.  bf16 tensors are numpy uint16 arrays of bit patterns.  PARI
 reference ships no golden vectors for this path (see the header of oracle.c).
 """
 import ctypes as C
+import hashlib
 import os
 import subprocess
 
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB = os.path.join(HERE, "liboracle.so")
+
+
+def _cpu_tag():
+    """Digest of this host's CPU feature flags: the library is built -march=native, so a build made
+    on another kind of CPU must not be loaded here."""
+    flags = ""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    flags = line
+                    break
+    except OSError:
+        pass
+    return hashlib.sha1(flags.encode()).hexdigest()[:10]
+
+
+TAG = _cpu_tag()
+LIB = os.path.join(HERE, f"liboracle_{TAG}.so")
 
 UNARY = {"none": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "relu": 4, "sigmoid": 5, "exp": 6}
 PAIR = {"none": 0, "swiglu": 1, "geglu": 2, "rope": 3, "swap": 4}
@@ -22,7 +41,8 @@ _lib = None
 def build(force=False):
     src = os.path.join(HERE, "oracle.c")
     if force or not os.path.exists(LIB) or os.path.getmtime(LIB) < os.path.getmtime(src):
-        subprocess.check_call(["make", "-C", HERE, "-B" if force else "-s"], stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-C", HERE, f"TAG={TAG}", "-B" if force else "-s"],
+                              stdout=subprocess.DEVNULL)
     return LIB
 
 
@@ -42,6 +62,12 @@ def _p(a):
 
 def num_threads():
     return lib().xo_num_threads()
+
+
+def set_num_threads(n):
+    """OpenMP threads the oracle's loops use from now on (launchers such as torch.distributed.run
+    export OMP_NUM_THREADS=1, which would otherwise stick)."""
+    lib().xo_set_num_threads(int(n))
 
 
 def f32_to_bf16(x):

@@ -349,6 +349,14 @@ int main(int argc, const char** argv) {
                               const float s = rowv(l, m);
                               return silu(a[ev] * s * Cv[size_t(l) * N + ev]) * (a[ev + 1] * s * Cv[size_t(l) * N + ev + 1]);
                             });
+  } else if (p == "w8a8_geglu") {
+    using Kt = xe_fuse::GemmDequantGeGLU<>;
+    ok = run_case<Kt::Gemm>(P, buf, Kt::make_evt_args(buf.row.get(), M, buf.col.get(), N), true,
+                            [&](int l, int m, int n, const float* a) {
+                              const int ev = n & ~1;
+                              const float s = rowv(l, m);
+                              return gelu(a[ev] * s * Cv[size_t(l) * N + ev]) * (a[ev + 1] * s * Cv[size_t(l) * N + ev + 1]);
+                            });
   } else if (p == "unsupported") {
     // a tree outside the flat program must be refused, not run: gamma[n] applied after GeLU
     using EVT = b::ScaleCols<b::GeLU<b::Acc>, TileShape, float>;

@@ -65,4 +65,7 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XEFUSE_REFERENCE_ROOT", "/root/reference"))
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XEFUSE_REFERENCE_ROOT")
+    if not ref_root:
+        sys.exit("usage: make_golden.py <reference checkout>   (or set XEFUSE_REFERENCE_ROOT)")
+    main(ref_root)

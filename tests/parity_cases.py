@@ -15,7 +15,7 @@ RTOL = 1e-2
 PRESETS = ["k1", "k1v2", "k2", "k2_compact", "k2_geglu", "k2v2", "k3", "k4", "k4v2", "k4v2_table",
            "k0a", "k0_dual", "w8a8_dequant", "w8a8_dequant_biased", "w8a8_biased_bf16bias",
            "bias_gelu", "bias_gelu_tanh", "scale_silu", "relu", "sigmoid", "w8a8_rope", "w8a8_swiglu",
-           "identity"]
+           "w8a8_geglu", "identity"]
 
 
 def is_int8(preset):
@@ -77,6 +77,8 @@ def epilogue_kwargs(o, preset, d):
         k = dict(row=d["scale_token"], col=d["scale_channel"], pair="rope", cos_sin=d["cos_sin_full"])
     elif preset == "w8a8_swiglu":
         k = dict(row=d["scale_token"], col=d["scale_channel"], pair="swiglu")
+    elif preset == "w8a8_geglu":      # DequantGeGLU, builder/epilogue_builder.hpp:276-280
+        k = dict(row=d["scale_token"], col=d["scale_channel"], pair="geglu")
     elif preset == "bias_gelu":
         k = dict(bias=d["bias"], unary="gelu")
     elif preset == "bias_gelu_tanh":

@@ -28,7 +28,8 @@ def test_select_tile_keeps_the_reference_interface():
         assert re.fullmatch(r"_\d+, _\d+, _\d+", out), out
         assert {int(x.strip().lstrip("_")) for x in out.split(",")} <= extents   # only known extents
     assert ts.select_tile(4096, 28672, 4096, "k2") == "_256, _256, _32"
-    assert ts.select_tile(512, 4096, 4096, "k1") == "_128, _128, _32"
+    assert ts.select_tile(512, 4096, 4096, "k1") == "_256, _256, _32"      # cluster split-K variant
+    assert ts.kernel_name(512, 4096, 4096) == "bf16_256x256_cta2_k128_kc2"
     assert ts.native_tile(8192, 8192, 28672, "s8") == (256, 256, 2, 256)
 
 
@@ -37,6 +38,7 @@ def test_selector_mirrors_the_library_choice(capi, cuda):
     import torch
     ts = _selector()
     sms = torch.cuda.get_device_properties(cuda).multi_processor_count
+    cap = {"bf16": capi.cluster_capacity(capi.DT_BF16), "s8": capi.cluster_capacity(capi.DT_S8)}
     for (M, N, K) in [(4096, 28672, 4096), (4096, 4096, 4096), (4096, 1024, 4096), (512, 4096, 4096),
                       (128, 512, 256), (8192, 3584, 4096), (1024, 2048, 1024), (4096, 7168, 4096),
                       (128, 4096, 4096), (4096, 512, 14336), (128, 256, 8192)]:
@@ -46,7 +48,8 @@ def test_selector_mirrors_the_library_choice(capi, cuda):
             D = torch.zeros((M, N), dtype=torch.bfloat16, device=cuda)
             plan = capi.GemmPlan(A, B, D)
             # the library's name also carries the pipeline depth ("_s3"), which the mirror leaves out
-            assert re.sub(r"_s\d+", "", plan.kernel_name) == ts.kernel_name(M, N, K, dt, sm_count=sms), (M, N, K, dt)
+            want = ts.kernel_name(M, N, K, dt, sm_count=sms, pairs=cap[dt][0], quads=cap[dt][1])
+            assert re.sub(r"_s\d+(?=_|$)", "", plan.kernel_name) == want, (M, N, K, dt)
 
 
 def test_split_planner_invariants():
@@ -59,7 +62,11 @@ def test_split_planner_invariants():
     for M, N, K in itertools.product([128, 512, 2048, 4096, 8192], [256, 1024, 3584, 7168, 28672],
                                      [256, 1024, 4096, 14336]):
         for dt, es, variants in (("bf16", 2, ts.BF16_VARIANTS), ("s8", 1, ts.S8_VARIANTS)):
-            rows, bn, ctas, kstage, split = ts.native_tile(M, N, K, dt, with_split=True)
+            rows, bn, ctas, kstage, split, kc = ts.native_tile(M, N, K, dt, with_split=True)
+            if kc > 1:        # cluster split-K: whole tiles, one per cluster, no global split
+                assert split == 0 and -(-M // rows) * -(-N // bn) <= ts.SM_COUNT // 4
+                assert -(-K // kstage) >= ts.MIN_KB_PER_GROUP * kc
+                continue
             units = ts.SM_COUNT // ctas
             tiles = -(-M // rows) * -(-N // bn)
             if split:

@@ -19,7 +19,7 @@ CPP = os.path.join(ROOT, "tests", "cpp")
 BUILD = os.path.join(CPP, "build")
 FE = os.path.join(ROOT, "xe-fuse_b200", "include")
 LIBDIR = os.path.join(ROOT, "xe-fuse_b200")
-REF = os.environ.get("XEFUSE_REFERENCE_ROOT", "/root/reference")   # a checkout of the reference, if any
+REF = os.environ.get("XEFUSE_REFERENCE_ROOT", "")   # a checkout of the reference, if any
 CUDA = "/usr/local/cuda"
 
 
@@ -143,7 +143,7 @@ def test_reference_test_mains_compile_unmodified(capi, tmp_path):
 
 
 HARNESS_PRESETS = ["k1", "k1v2", "k2", "k2_compact", "k2_geglu", "k2v2", "k8", "k3", "k4", "k4v2", "k0a", "k0",
-                   "bias_gelu", "w8a8", "w8a8_biased", "w8a8_rope", "w8a8_swiglu", "unsupported"]
+                   "bias_gelu", "w8a8", "w8a8_biased", "w8a8_rope", "w8a8_swiglu", "w8a8_geglu", "unsupported"]
 
 
 @pytest.mark.gpu

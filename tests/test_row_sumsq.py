@@ -54,7 +54,8 @@ def test_row_sumsq_every_variant(flags_name, capi, oracle, cuda):
 
 def test_row_sumsq_with_split_k(capi, oracle, cuda):
     """Units of a split tile are finished by different CTAs; each slot is still written once."""
-    plan, _, _ = _run(capi, oracle, cuda, 640, 2048, 6144, seed=33, flags=_variant_flags(capi, "2cta_bn256"))
+    plan, _, _ = _run(capi, oracle, cuda, 640, 2048, 6144, seed=33,
+                      flags=_variant_flags(capi, "2cta_bn256") | capi.FLAG_NO_CLUSTER_SPLIT)
     assert "ksplit" in plan.kernel_name
 
 

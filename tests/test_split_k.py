@@ -29,14 +29,14 @@ pytestmark = pytest.mark.gpu
 ])
 def test_split_presets(preset, shape, flags_name, capi, oracle, cuda):
     M, N, K = shape
-    plan = check(capi, oracle, preset, M, N, K, cuda, flags=_variant_flags(capi, flags_name))
+    plan = check(capi, oracle, preset, M, N, K, cuda, flags=(_variant_flags(capi, flags_name) | capi.FLAG_NO_CLUSTER_SPLIT))
     assert "ksplit" in plan.kernel_name, plan.kernel_name
 
 
 @pytest.mark.parametrize("flags_name", ["1cta_bn128_ks1", "1cta_bn128_ks2", "1cta_bn256_ks1", "2cta_bn128_ks2",
                                         "2cta_bn256_ks1", "direct"])
 def test_split_every_variant(flags_name, capi, oracle, cuda):
-    plan = check(capi, oracle, "k2_compact", 384, 2304, 6144, cuda, flags=_variant_flags(capi, flags_name))
+    plan = check(capi, oracle, "k2_compact", 384, 2304, 6144, cuda, flags=(_variant_flags(capi, flags_name) | capi.FLAG_NO_CLUSTER_SPLIT))
     assert "ksplit" in plan.kernel_name, plan.kernel_name
 
 
@@ -52,7 +52,7 @@ def test_split_int32_bit_exact_and_repeatable(shape, flags_name, capi, oracle, c
     B = rng.integers(-128, 128, (K, N), dtype=np.int8)
     want = oracle.gemm_s8(A, B)
     D = torch.empty((M, N), dtype=torch.int32, device=cuda)
-    flags = _variant_flags(capi, flags_name)
+    flags = (_variant_flags(capi, flags_name) | capi.FLAG_NO_CLUSTER_SPLIT)
     plan = capi.GemmPlan(torch.from_numpy(A).to(cuda), torch.from_numpy(B).to(cuda), D, flags=flags)
     assert "ksplit" in plan.kernel_name, plan.kernel_name
     for _ in range(3):
@@ -79,7 +79,7 @@ def test_split_bf16_is_deterministic(capi, oracle, cuda):
     A = torch.from_numpy(d["A"].view(np.int16)).view(torch.bfloat16).to(cuda)
     B = torch.from_numpy(d["B"].view(np.int16)).view(torch.bfloat16).to(cuda)
     D = torch.empty((512, 2048), dtype=torch.bfloat16, device=cuda)
-    plan = capi.GemmPlan(A, B, D)
+    plan = capi.GemmPlan(A, B, D, flags=capi.FLAG_NO_CLUSTER_SPLIT)
     assert "ksplit" in plan.kernel_name
     outs = []
     for _ in range(4):
@@ -98,7 +98,7 @@ def test_small_workspace_falls_back_to_whole_tiles(capi, oracle, cuda):
     A = torch.from_numpy(d["A"].view(np.int16)).view(torch.bfloat16).to(cuda)
     B = torch.from_numpy(d["B"].view(np.int16)).view(torch.bfloat16).to(cuda)
     D = torch.empty((512, 2048), dtype=torch.bfloat16, device=cuda)
-    plan = capi.GemmPlan(A, B, D)
+    plan = capi.GemmPlan(A, B, D, flags=capi.FLAG_NO_CLUSTER_SPLIT)
     desc = capi.XfGemmDesc.from_buffer_copy(plan.desc)
     desc.workspace_bytes = 0
     ws = torch.zeros(16, dtype=torch.uint8, device=cuda)
@@ -125,7 +125,7 @@ def test_split_wait_gives_up_and_the_plan_recovers(capi, oracle, cuda):
     A = torch.from_numpy(d["A"].view(np.int16)).view(torch.bfloat16).to(cuda)
     B = torch.from_numpy(d["B"].view(np.int16)).view(torch.bfloat16).to(cuda)
     D = torch.empty((512, 2048), dtype=torch.bfloat16, device=cuda)
-    plan = capi.GemmPlan(A, B, D, flags=capi.FLAG_SHORT_WAITS)
+    plan = capi.GemmPlan(A, B, D, flags=capi.FLAG_SHORT_WAITS | capi.FLAG_NO_CLUSTER_SPLIT)
     assert "ksplit" in plan.kernel_name
     plan.run()
     torch.cuda.synchronize()

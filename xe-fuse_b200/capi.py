@@ -21,7 +21,10 @@ FLAG_NO_SPLIT = 128
 FLAG_NO_PDL = 4096
 FLAG_SHORT_WAITS = 8192
 FLAG_NO_TAIL_HELP = 32768
-FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA = 256, 512
+FLAG_NO_CLUSTER_SPLIT, FLAG_FORCE_CLUSTER_SPLIT = 65536, 131072
+# timing diagnostics (D is garbage): honoured only with XEFUSE_ALLOW_DIAG=1 in the environment
+FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA, FLAG_DIAG_NO_EPILOGUE, FLAG_DIAG_NO_STORE = 256, 512, 1024, 2048
+STATIC_WORKSPACE_BYTES = 2097152
 
 STATUS_NAMES = ["XF_SUCCESS", "XF_ERR_MISALIGNED_OPERAND", "XF_ERR_INVALID_DATA_TYPE",
                 "XF_ERR_INVALID_LAYOUT", "XF_ERR_INVALID_PROBLEM", "XF_ERR_NOT_SUPPORTED",
@@ -69,7 +72,7 @@ class XfGemmDesc(C.Structure):
 EXPORTS = [
     "xf_gemm_can_implement", "xf_gemm_workspace_size", "xf_gemm_plan_create", "xf_gemm_run",
     "xf_gemm_plan_device_status", "xf_gemm_plan_kernel_name", "xf_plan_destroy",
-    "xf_gemm_run_static_workspace",
+    "xf_gemm_run_static_workspace", "xf_gemm_static_workspace_status", "xf_gemm_cluster_capacity",
     "xf_last_error_string", "xf_status_string", "xf_version", "xf_compiled_arch",
     "xf_sa_scale_rows", "xf_sa_scale_cols", "xf_sa_add_residual", "xf_sa_residual_gamma",
     "xf_sa_swiglu", "xf_sa_geglu", "xf_sa_rope", "xf_sa_rope_scaled", "xf_sa_unary",
@@ -102,6 +105,8 @@ def lib():
     L.xf_gemm_plan_kernel_name.restype = C.c_char_p
     L.xf_plan_destroy.argtypes = [vp]
     L.xf_gemm_run_static_workspace.argtypes = [C.POINTER(XfGemmDesc), vp]
+    L.xf_gemm_static_workspace_status.argtypes = [C.POINTER(C.c_int32)]
+    L.xf_gemm_cluster_capacity.argtypes = [i32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     L.xf_last_error_string.restype = C.c_char_p
     L.xf_status_string.argtypes = [i32]
     L.xf_status_string.restype = C.c_char_p
@@ -241,6 +246,13 @@ class GemmPlan:
             self.close()
         except Exception:
             pass
+
+
+def cluster_capacity(dtype_code=DT_BF16):
+    """(CTA pairs, 4-CTA clusters) the current device holds at once: the planner's scheduling units."""
+    pairs, quads = C.c_int32(0), C.c_int32(0)
+    check(lib().xf_gemm_cluster_capacity(dtype_code, C.byref(pairs), C.byref(quads)))
+    return pairs.value, quads.value
 
 
 def _stream():

@@ -72,29 +72,31 @@ static bool encode_3d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base,
 typedef void (*KernelFn)(const GemmParams);
 
 struct Variant {
-  int kind, bn, ctas, ks, stages, smem;
+  int kind, bn, ctas, ks, kc, stages, smem;
   KernelFn fn;
   const char* name;
 };
 
-#define XF_VARIANT(KIND, BN, CTAS, KS, NAME)                                                     \
-  {KIND, BN, CTAS, KS, TileCfg<KIND, BN, CTAS, KS>::STAGES, TileCfg<KIND, BN, CTAS, KS>::SMEM_BYTES, \
-   gemm_evt_kernel<KIND, BN, CTAS, KS>, NAME}
+#define XF_VARIANT(KIND, BN, CTAS, KS, KC, NAME)                                      \
+  {KIND, BN, CTAS, KS, KC, TileCfg<KIND, BN, CTAS, KS, KC>::STAGES,                    \
+   TileCfg<KIND, BN, CTAS, KS, KC>::SMEM_BYTES, gemm_evt_kernel<KIND, BN, CTAS, KS, KC>, NAME}
 
-// name = <dtype>_<cluster rows>x<columns>_cta<CTAs per tile>_k<K elements per stage>
+// name = <dtype>_<tile rows>x<columns>_cta<CTAs per MMA>_k<K elements per stage>[_kc<K groups per cluster>]
 static const Variant g_variants[] = {
-    XF_VARIANT(0, 256, 2, 1, "bf16_256x256_cta2_k64"),
-    XF_VARIANT(0, 256, 2, 2, "bf16_256x256_cta2_k128"),
-    XF_VARIANT(0, 256, 1, 1, "bf16_128x256_cta1_k64"),
-    XF_VARIANT(0, 128, 2, 1, "bf16_256x128_cta2_k64"),
-    XF_VARIANT(0, 128, 2, 2, "bf16_256x128_cta2_k128"),
-    XF_VARIANT(0, 128, 1, 1, "bf16_128x128_cta1_k64"),
-    XF_VARIANT(0, 128, 1, 2, "bf16_128x128_cta1_k128"),
-    XF_VARIANT(1, 256, 2, 1, "s8_256x256_cta2_k128"),
-    XF_VARIANT(1, 256, 2, 2, "s8_256x256_cta2_k256"),
-    XF_VARIANT(1, 256, 1, 1, "s8_128x256_cta1_k128"),
-    XF_VARIANT(1, 128, 1, 1, "s8_128x128_cta1_k128"),
-    XF_VARIANT(1, 128, 1, 2, "s8_128x128_cta1_k256"),
+    XF_VARIANT(0, 256, 2, 1, 1, "bf16_256x256_cta2_k64"),
+    XF_VARIANT(0, 256, 2, 2, 1, "bf16_256x256_cta2_k128"),
+    XF_VARIANT(0, 256, 1, 1, 1, "bf16_128x256_cta1_k64"),
+    XF_VARIANT(0, 128, 2, 1, 1, "bf16_256x128_cta2_k64"),
+    XF_VARIANT(0, 128, 2, 2, 1, "bf16_256x128_cta2_k128"),
+    XF_VARIANT(0, 128, 1, 1, 1, "bf16_128x128_cta1_k64"),
+    XF_VARIANT(0, 128, 1, 2, 1, "bf16_128x128_cta1_k128"),
+    XF_VARIANT(0, 256, 2, 2, 2, "bf16_256x256_cta2_k128_kc2"),
+    XF_VARIANT(1, 256, 2, 1, 1, "s8_256x256_cta2_k128"),
+    XF_VARIANT(1, 256, 2, 2, 1, "s8_256x256_cta2_k256"),
+    XF_VARIANT(1, 256, 1, 1, 1, "s8_128x256_cta1_k128"),
+    XF_VARIANT(1, 128, 1, 1, 1, "s8_128x128_cta1_k128"),
+    XF_VARIANT(1, 128, 1, 2, 1, "s8_128x128_cta1_k256"),
+    XF_VARIANT(1, 256, 2, 2, 2, "s8_256x256_cta2_k256_kc2"),
 };
 static const int g_num_variants = sizeof(g_variants) / sizeof(g_variants[0]);
 
@@ -106,6 +108,8 @@ struct xf_plan {
   int grid;
   int device;
   int no_pdl;   // 1: launch without programmatic stream serialization
+  size_t workspace_used;   // bytes of the workspace the plan's kernel touches
+  size_t clear_bytes;      // leading bytes (status word, split counters) that must be zero before a launch
   char name[64];
 };
 
@@ -155,6 +159,14 @@ static xf_status validate(const xf_gemm_desc* d) {
   if (d->dtype_ab != XF_DT_BF16 && d->dtype_ab != XF_DT_S8) {
     set_error("A/B dtype must be bf16 or int8 (got %d)", d->dtype_ab);
     return XF_ERR_INVALID_DATA_TYPE;
+  }
+  if (d->flags & XF_FLAG_DIAG_MASK) {
+    const char* allow = getenv("XEFUSE_ALLOW_DIAG");
+    if (!allow || allow[0] != '1') {
+      set_error("the XF_FLAG_DIAG_* flags make D garbage; they are honoured only with XEFUSE_ALLOW_DIAG=1 "
+                "in the environment");
+      return XF_ERR_NOT_SUPPORTED;
+    }
   }
   if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->L <= 0) {
     set_error("problem extents must be positive (M=%d N=%d K=%d L=%d)", d->M, d->N, d->K, d->L);
@@ -311,6 +323,20 @@ static double tile_time_us(const Variant& v, int K, int es) {
   return (2.0 + 0.0029 * K * es) * (v.bn / 256.0) / variant_eff(v);
 }
 
+// Cluster split-K (variants with kc > 1): the kc CTA pairs of a cluster each run 1/kc of one tile's
+// K range and swap partial accumulators through distributed shared memory, about a microsecond.
+// One tile per cluster, so the problem must fit the clusters the device can hold at once, and
+// every pair needs a few K blocks to fill its pipeline.
+static const double kClusterExchangeUs = 1.0;
+static const int kMinKbPerGroup = 4;
+static bool cluster_split_fits(const Variant& v, const xf_gemm_desc* d, int tiles, int max_clusters) {
+  const int es = d->dtype_ab == XF_DT_BF16 ? 2 : 1;
+  const int num_kb = (d->K + (128 / es) * v.ks - 1) / ((128 / es) * v.ks);
+  if (num_kb < kMinKbPerGroup * v.kc) return false;
+  if (d->flags & XF_FLAG_FORCE_CLUSTER_SPLIT) return true;   // more tiles than clusters only queue
+  return tiles <= max_clusters;
+}
+
 // Split-K of the remainder wave.  With T tiles on U scheduling units, the last wave holds
 // T % U tiles and leaves the other units idle; cutting each of those tiles into S K slices fills
 // S times as many units for 1/S of the time, at the price of passing the partial accumulators
@@ -345,7 +371,7 @@ static int split_factor(const Variant& v, const xf_gemm_desc* d, int tiles, int 
 // Picks the CTA tile.  The caller's TileShape (an Intel Xe work-group tile) is only a hint; the
 // native tiles are {128,256} rows x {128,256} columns.  The estimate is whole waves x tile time
 // plus the remainder wave, whole or split.
-static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
+static const Variant* select_variant(const xf_gemm_desc* d, int sm_count, int max_quads) {
   const int kind = d->dtype_ab == XF_DT_BF16 ? 0 : 1;
   const int es = kind == 0 ? 2 : 1;
   const Variant* best = nullptr;
@@ -353,6 +379,19 @@ static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
   for (int i = 0; i < g_num_variants; ++i) {
     const Variant& v = g_variants[i];
     if (v.kind != kind) continue;
+    if (v.kc > 1) {
+      if (d->flags & (XF_FLAG_NO_CLUSTER_SPLIT | XF_FLAG_FORCE_1CTA | XF_FLAG_FORCE_BN128 | XF_FLAG_FORCE_KS1))
+        continue;
+      const int tiles = ceil_div(d->M, 128 * v.ctas) * ceil_div(d->N, v.bn) * d->L;
+      if (!cluster_split_fits(v, d, tiles, max_quads)) continue;
+      if (d->flags & XF_FLAG_FORCE_CLUSTER_SPLIT) return &v;
+      const double cost = tile_time_us(v, (d->K + v.kc - 1) / v.kc, es) + kClusterExchangeUs;
+      if (!best || cost < best_cost * 0.999) {
+        best = &v;
+        best_cost = cost;
+      }
+      continue;
+    }
     if ((d->flags & XF_FLAG_FORCE_1CTA) && v.ctas != 1) continue;
     if ((d->flags & XF_FLAG_FORCE_2CTA) && v.ctas != 2) continue;
     if ((d->flags & XF_FLAG_FORCE_BN128) && v.bn != 128) continue;
@@ -379,11 +418,50 @@ static const Variant* select_variant(const xf_gemm_desc* d, int sm_count) {
 // partial accumulators (256-byte aligned).
 struct Geometry {
   const Variant* v;
-  int dev, sm_count, units;
+  int dev, sm_count, units;   // units: CTAs / CTA pairs / clusters that run at once
   int total_tiles, num_kb;
   int split_s, split_tiles;
   size_t counters_off, partials_off, workspace_bytes;
 };
+
+// Clusters of variant v the current device can hold at once (0 if the query fails).
+static int active_clusters_of(const Variant& v, int sm_count) {
+  const int cl = v.ctas * v.kc;
+  if (cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           v.smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sm_count - (sm_count % cl), 1, 1);
+  cfg.blockDim = dim3(384, 1, 1);
+  cfg.dynamicSmemBytes = v.smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = cl; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int nclusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&nclusters, reinterpret_cast<const void*>(v.fn), &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return nclusters;
+}
+
+// Co-resident clusters of the cluster split-K variant (kc K groups) of one input type on device
+// `dev`; looked up once per device and kind.
+static int max_active_clusters(int kind, int kc, int dev, int sm_count) {
+  static std::mutex mu;
+  static int cache[64][2];   // 0 = not looked up yet, -1 = none
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && dev < 64 && cache[dev][kind] != 0) return cache[dev][kind] < 0 ? 0 : cache[dev][kind];
+  int n = 0;
+  for (int i = 0; i < g_num_variants; ++i)
+    if (g_variants[i].kind == kind && g_variants[i].kc == kc) n = active_clusters_of(g_variants[i], sm_count);
+  if (dev >= 0 && dev < 64) cache[dev][kind] = n > 0 ? n : -1;
+  return n;
+}
 
 static xf_status plan_geometry(const xf_gemm_desc* d, Geometry* g) {
   memset(g, 0, sizeof(*g));
@@ -399,7 +477,7 @@ static xf_status plan_geometry(const xf_gemm_desc* d, Geometry* g) {
     set_error("this library holds sm_100a code only; device %d has compute capability %d.x", dev, major);
     return XF_ERR_ARCH_MISMATCH;
   }
-  const Variant* v = select_variant(d, sm_count);
+  const Variant* v = select_variant(d, sm_count, max_active_clusters(d->dtype_ab == XF_DT_BF16 ? 0 : 1, 2, dev, sm_count));
   if (!v) {
     set_error("no kernel variant matches the requested flags");
     return XF_ERR_NOT_SUPPORTED;
@@ -414,27 +492,14 @@ static xf_status plan_geometry(const xf_gemm_desc* d, Geometry* g) {
   const int es = elem_size(d->dtype_ab);
   g->num_kb = ceil_div(d->K, (128 / es) * v->ks);
   g->total_tiles = ceil_div(d->M, 128 * v->ctas) * ceil_div(d->N, v->bn) * d->L;
-  int units = sm_count / v->ctas;
-  if (v->ctas == 2) {
-    // number of CTA pairs that can be co-resident (GPC boundaries may leave an SM unpaired)
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(sm_count - (sm_count & 1), 1, 1);
-    cfg.blockDim = dim3(384, 1, 1);
-    cfg.dynamicSmemBytes = v->smem;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    int nclusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&nclusters, reinterpret_cast<const void*>(v->fn), &cfg) ==
-            cudaSuccess && nclusters > 0)
-      units = nclusters;
-    else
-      cudaGetLastError();
+  int units = sm_count / (v->ctas * v->kc);
+  if (v->ctas * v->kc > 1) {
+    // clusters that can be co-resident (GPC boundaries may leave SMs outside any cluster)
+    const int n = active_clusters_of(*v, sm_count);
+    if (n > 0) units = n;
   }
   g->units = units;
-  g->split_s = split_factor(*v, d, g->total_tiles, units);
+  g->split_s = v->kc > 1 ? 0 : split_factor(*v, d, g->total_tiles, units);
   g->split_tiles = g->split_s ? g->total_tiles % units : 0;
   g->counters_off = 256;
   const size_t counters = static_cast<size_t>(g->split_tiles) * v->ctas * 8 * sizeof(int);
@@ -444,11 +509,40 @@ static xf_status plan_geometry(const xf_gemm_desc* d, Geometry* g) {
   return XF_SUCCESS;
 }
 
+// Zeroes `bytes` of device memory and returns only once that has happened.  A plain cudaMemset of
+// device memory is queued on the legacy default stream and may still be pending when the caller
+// launches on a non-blocking stream of its own; here the clear runs on a private non-blocking
+// stream per device and is waited for.
+static cudaError_t clear_now(void* ptr, size_t bytes, int dev) {
+  static std::mutex mu;
+  static cudaStream_t streams[64];
+  cudaStream_t st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!streams[dev]) {
+      cudaError_t e = cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking);
+      if (e != cudaSuccess) return e;
+    }
+    st = streams[dev];
+  }
+  cudaError_t e = cudaMemsetAsync(ptr, 0, bytes, st);
+  if (e != cudaSuccess) return e;
+  return cudaStreamSynchronize(st);
+}
+
 static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* plan,
-                            bool clear_status_now = true) {
+                            bool clear_status_now = true, bool strict_workspace = false) {
   Geometry g;
   xf_status gs = plan_geometry(d, &g);
   if (gs != XF_SUCCESS) return gs;
+  if (strict_workspace && g.workspace_bytes > d->workspace_bytes) {
+    set_error("this problem's schedule cuts the tiles of its last wave into %d K slices and needs %zu bytes "
+              "of workspace; only %llu are available here.  Set XF_FLAG_NO_SPLIT to run whole tiles (16 "
+              "bytes), or allocate a workspace and use xf_gemm_plan_create / xf_gemm_run",
+              g.split_s, g.workspace_bytes, (unsigned long long)d->workspace_bytes);
+    return XF_ERR_NOT_SUPPORTED;
+  }
   if (g.split_s && (!workspace || d->workspace_bytes < g.workspace_bytes || !aligned16(workspace))) {
     // the caller did not promise room for the partial accumulators: whole tiles only.  The tile
     // variant may differ from the one a split would have chosen, so select again.
@@ -472,7 +566,27 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
   p.tiles_m = ceil_div(d->M, 128 * v->ctas);
   p.tiles_n = ceil_div(d->N, v->bn);
   p.num_kb = ceil_div(d->K, kblk);
-  p.group_m = (v->ctas == 2) ? 8 : 16;
+  // Rasterisation: tiles run M-fastest inside groups of group_m row tiles, so the units that run
+  // together share B panels and a group's A panels are read again by every following wave of the
+  // group.  The group is as tall as the A panels that fit a share of L2 (fewer passes over B).
+  {
+    int l2 = 0;
+    cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
+    const double panel = static_cast<double>(128 * v->ctas) * d->K * es;   // bytes of one row tile's A panel
+    int gm = static_cast<int>(0.40 * l2 / (panel > 1 ? panel : 1));
+    if (gm < 4) gm = 4;
+    if (gm > p.tiles_m) gm = p.tiles_m;
+    if (const char* eg = getenv("XEFUSE_GROUP_M")) {   // tuning override
+      const int v2 = atoi(eg);
+      if (v2 > 0) gm = v2;
+    }
+    p.group_m = gm;
+    p.l2_hint_a = p.l2_hint_b = 0;
+    if (const char* eh = getenv("XEFUSE_L2_HINTS")) {  // tuning override: "<a><b>", 0 none 1 last 2 first
+      if (eh[0] >= '0' && eh[0] <= '2') p.l2_hint_a = eh[0] - '0';
+      if (eh[0] && eh[1] >= '0' && eh[1] <= '2') p.l2_hint_b = eh[1] - '0';
+    }
+  }
   p.a_batched = (d->L > 1 && d->batch_a != 0) ? 1 : 0;
   p.b_batched = (d->L > 1 && d->batch_b != 0) ? 1 : 0;
   p.D = d->D; p.ldd = d->ldd; p.batch_d = d->batch_d;
@@ -499,7 +613,7 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
                             (d->batch_d * 2) % 16 == 0 && !(d->flags & XF_FLAG_DIRECT_STORE);
   p.direct_store = tma_store_ok ? 0 : 1;
   p.diag = ((d->flags & XF_FLAG_DIAG_NO_LOAD) ? 1 : 0) | ((d->flags & XF_FLAG_DIAG_NO_MMA) ? 2 : 0) |
-           ((d->flags & XF_FLAG_DIAG_NO_EPILOGUE) ? 4 : 0) | ((d->flags & 2048) ? 8 : 0) |
+           ((d->flags & XF_FLAG_DIAG_NO_EPILOGUE) ? 4 : 0) | ((d->flags & XF_FLAG_DIAG_NO_STORE) ? 8 : 0) |
            ((d->flags & XF_FLAG_NO_TAIL_HELP) ? 16 : 0);
 
   const CUtensorMapDataType dt =
@@ -543,16 +657,19 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
     p.split_counters = reinterpret_cast<int*>(static_cast<char*>(workspace) + g.counters_off);
     p.split_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + g.partials_off);
   }
-  const int nunits = p.total_items < g.units ? p.total_items : g.units;
-  plan->grid = nunits * v->ctas;
+  // cluster split-K runs one tile per cluster (clusters beyond the co-resident ones queue)
+  const int nunits = (v->kc > 1 || p.total_items < g.units) ? p.total_items : g.units;
+  plan->grid = nunits * v->ctas * v->kc;
   cudaError_t ce;
+  plan->workspace_used = g.split_s ? g.workspace_bytes : 16;
+  plan->clear_bytes = g.split_s ? g.partials_off : 16;
   if (g.split_s)
     snprintf(plan->name, sizeof(plan->name), "%s_s%d_ksplit%d", v->name, v->stages, g.split_s);
   else
     snprintf(plan->name, sizeof(plan->name), "%s_s%d", v->name, v->stages);
   if (p.status && clear_status_now) {
     // the status word, and the split counters: each launch leaves them at zero again
-    ce = cudaMemset(p.status, 0, g.split_s ? g.partials_off : 16);
+    ce = clear_now(p.status, g.split_s ? g.partials_off : 16, dev);
     if (ce != cudaSuccess) {
       set_error("clearing the workspace status word failed: %s", cudaGetErrorString(ce));
       return XF_ERR_INTERNAL;
@@ -613,6 +730,11 @@ xf_status xf_gemm_run(xf_plan* plan, void* stream) {
     xf::set_error("null plan");
     return XF_ERR_INVALID_PROBLEM;
   }
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess || cur != plan->device) {
+    xf::set_error("plan %s was created on device %d but device %d is current", plan->name, plan->device, cur);
+    return XF_ERR_INVALID_PROBLEM;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(plan->grid, 1, 1);
   cfg.blockDim = dim3(384, 1, 1);
@@ -620,7 +742,7 @@ xf_status xf_gemm_run(xf_plan* plan, void* stream) {
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = plan->variant->ctas;
+  attr[0].val.clusterDim.x = plan->variant->ctas * plan->variant->kc;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   // programmatic dependent launch: this kernel's set-up may overlap the tail of the previous
@@ -640,14 +762,15 @@ xf_status xf_gemm_run(xf_plan* plan, void* stream) {
 // ---------------------------------------------------------------------------------------------
 // xf_gemm_run_static_workspace: the fused GEMM for callers that may not allocate.
 //
-// The kernel's scratch (the status word a bounded wait writes when it gives up) normally lives in
-// a workspace the caller allocates.  Here it lives in the file-scope device array below, which
-// every GPU that loads this library holds until the process exits.  Nothing in this entry point
-// allocates: the plan is built on the stack, the array's device address comes from
+// The kernel's scratch -- the status word a bounded wait writes when it gives up and, when the
+// tiles of the last wave are cut into K slices, the slice counters and partial accumulators --
+// normally lives in a workspace the caller allocates.  Here it lives in the file-scope device array
+// below, which every GPU that loads this library holds until the process exits.  Nothing in this
+// entry point allocates: the plan is built on the stack, the array's device address comes from
 // cudaGetSymbolAddress (host code must not pass the array's name to a kernel: on the host that
-// name is only a stand-in, not a device address), and the word is cleared with a memset ordered on
-// the caller's stream.  All calls on one device share the array, so two calls whose kernels overlap
-// on the GPU race on it.
+// name is only a stand-in, not a device address), and the words that must start at zero are
+// cleared with a memset ordered on the caller's stream.  All calls on one device share the array,
+// so two calls whose kernels overlap on the GPU race on it.
 static __device__ __align__(256) unsigned char g_static_workspace[XF_STATIC_WORKSPACE_BYTES];
 
 static const int kMaxDevices = 64;
@@ -656,7 +779,7 @@ static bool g_static_ws_ready[kMaxDevices];
 static std::mutex g_static_ws_mutex;
 
 // Device address of g_static_workspace on the CURRENT device; looked up once per device.
-static xf_status static_workspace_address(void** out) {
+static xf_status static_workspace_address(void** out, int* dev_out = nullptr) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) {
@@ -681,39 +804,59 @@ static xf_status static_workspace_address(void** out) {
     g_static_ws_ready[dev] = true;
   }
   *out = g_static_ws_addr[dev];
+  if (dev_out) *dev_out = dev;
   return XF_SUCCESS;
 }
 
 xf_status xf_gemm_run_static_workspace(const xf_gemm_desc* caller_desc, void* stream) {
   xf_status s = xf::validate(caller_desc);
   if (s != XF_SUCCESS) return s;
-  // The split of the remainder wave needs megabytes of scratch; this entry runs whole tiles only.
-  xf_gemm_desc local = *caller_desc;
-  local.flags |= XF_FLAG_NO_SPLIT;
-  const xf_gemm_desc* desc = &local;
-  size_t need = 0;
-  s = xf_gemm_workspace_size(desc, &need);
-  if (s != XF_SUCCESS) return s;
-  if (need > XF_STATIC_WORKSPACE_BYTES) {
-    xf::set_error("this problem needs %zu bytes of workspace; the static workspace holds at most %d. "
-                  "Allocate a workspace and use xf_gemm_plan_create / xf_gemm_run instead",
-                  need, XF_STATIC_WORKSPACE_BYTES);
-    return XF_ERR_NOT_SUPPORTED;
-  }
   void* ws = nullptr;
   s = static_workspace_address(&ws);
   if (s != XF_SUCCESS) return s;
+  // The array is the whole workspace this call may use.  A schedule that needs more (a split of
+  // the last wave whose partial accumulators do not fit) is refused by build_plan, not quietly
+  // replaced: the caller decides between XF_FLAG_NO_SPLIT and a workspace of its own.
+  xf_gemm_desc local = *caller_desc;
+  local.workspace_bytes = XF_STATIC_WORKSPACE_BYTES;
   xf_plan plan;  // on the stack: no host allocation either
   memset(&plan, 0, sizeof(plan));
-  s = xf::build_plan(desc, ws, &plan, /*clear_status_now=*/false);
+  s = xf::build_plan(&local, ws, &plan, /*clear_status_now=*/false, /*strict_workspace=*/true);
   if (s != XF_SUCCESS) return s;
-  // The array keeps whatever the previous call left: the status word must start at zero.
-  cudaError_t e = cudaMemsetAsync(ws, 0, 16, static_cast<cudaStream_t>(stream));
+  // The array keeps whatever the previous call left: the status word and the slice counters must
+  // start at zero (the partial accumulators are written before they are read).
+  cudaError_t e = cudaMemsetAsync(ws, 0, plan.clear_bytes, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     xf::set_error("clearing the static workspace failed: %s", cudaGetErrorString(e));
     return XF_ERR_INTERNAL;
   }
   return xf_gemm_run(&plan, stream);
+}
+
+xf_status xf_gemm_static_workspace_status(int32_t* device_code) {
+  if (!device_code) {
+    xf::set_error("null argument");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  *device_code = 0;
+  void* ws = nullptr;
+  int dev = 0;
+  xf_status s = static_workspace_address(&ws, &dev);
+  if (s != XF_SUCCESS) return s;
+  cudaError_t e = cudaMemcpy(device_code, ws, sizeof(int32_t), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) {
+    xf::set_error("reading the static workspace's status word failed: %s", cudaGetErrorString(e));
+    return XF_ERR_INTERNAL;
+  }
+  if (*device_code != 0) {
+    // reported once; the next xf_gemm_run_static_workspace clears the counters it uses anyway
+    e = cudaMemset(ws, 0, 16);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    xf::set_error("a kernel launched by xf_gemm_run_static_workspace gave up in a bounded wait (device code %d)",
+                  *device_code);
+    return XF_ERR_INTERNAL;
+  }
+  return XF_SUCCESS;
 }
 
 xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code) {
@@ -731,11 +874,7 @@ xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code) {
   if (*device_code != 0) {
     // reported once: clear the word, and the split counters a launch that gave up may have left
     // part-way, so the plan can run again
-    cudaMemset(plan->params.status, 0, 16);
-    if (plan->params.split_counters)
-      cudaMemset(plan->params.split_counters, 0,
-                 reinterpret_cast<char*>(plan->params.split_partials) -
-                     reinterpret_cast<char*>(plan->params.split_counters));
+    xf::clear_now(plan->params.status, plan->clear_bytes, plan->device);
     xf::set_error("kernel %s gave up in a bounded wait (device code %d)", plan->name, *device_code);
     return XF_ERR_INTERNAL;
   }
@@ -743,6 +882,31 @@ xf_status xf_gemm_plan_device_status(xf_plan* plan, int32_t* device_code) {
 }
 
 const char* xf_gemm_plan_kernel_name(const xf_plan* plan) { return plan ? plan->name : ""; }
+
+xf_status xf_gemm_cluster_capacity(int32_t dtype_ab, int32_t* pairs, int32_t* quads) {
+  if (!pairs || !quads || (dtype_ab != XF_DT_BF16 && dtype_ab != XF_DT_S8)) {
+    xf::set_error("cluster_capacity: bad arguments");
+    return XF_ERR_INVALID_PROBLEM;
+  }
+  int dev = 0, sm_count = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    xf::set_error("no CUDA device");
+    return XF_ERR_ARCH_MISMATCH;
+  }
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  const int kind = dtype_ab == XF_DT_BF16 ? 0 : 1;
+  *pairs = sm_count / 2;
+  for (int i = 0; i < xf::g_num_variants; ++i) {
+    const xf::Variant& v = xf::g_variants[i];
+    if (v.kind == kind && v.bn == 256 && v.ctas == 2 && v.ks == 2 && v.kc == 1) {
+      const int n = xf::active_clusters_of(v, sm_count);
+      if (n > 0) *pairs = n;
+    }
+  }
+  *quads = xf::max_active_clusters(kind, 2, dev, sm_count);
+  return XF_SUCCESS;
+}
 
 xf_status xf_plan_destroy(xf_plan* plan) {
   free(plan);

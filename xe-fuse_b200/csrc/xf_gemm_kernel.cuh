@@ -19,6 +19,12 @@
 // slices (GemmParams::split_s): the slices exchange raw accumulators through global memory and
 // share the finishing work (see the epilogue role).
 //
+// Small problems (at most one 256 x 256 tile per four SMs) use the cluster split-K variants
+// (KC == 2): a cluster holds KC CTA pairs that each accumulate one K range of the SAME tile into
+// their own TMEM; the pairs then swap partial accumulators through distributed shared memory
+// (st.shared::cluster into the partner's idle pipeline stages) and each pair finishes BN / KC of the
+// tile's columns.  No global scratch, no second launch.
+//
 // Shared memory per stage: A 128 rows x 128 B (K-major, 128-B swizzle) and B as BN/CTAS columns
 // split into 128-B column groups of KBLK rows each (MN-major, 128-B swizzle), exactly as the TMA
 // boxes land.  With CTAS == 2 each CTA loads its own 128 rows of A and its own half of the B
@@ -32,11 +38,13 @@
 
 namespace xf {
 
-template <int KIND, int BN_, int CTAS_, int KS_>
+template <int KIND, int BN_, int CTAS_, int KS_, int KC_ = 1>
 struct TileCfg {
   static constexpr int BN = BN_;
   static constexpr int CTAS = CTAS_;
   static constexpr int KS = KS_;                       // 128-byte K slabs per pipeline stage
+  static constexpr int KC = KC_;                       // CTA pairs of a cluster that share one tile's K range
+  static constexpr int CLUSTER = CTAS_ * KC_;          // CTAs per cluster
   static constexpr int BM = 128;                       // rows per CTA
   static constexpr int ES = (KIND == 0) ? 2 : 1;       // bytes per A/B element
   static constexpr int KSLAB = 128 / ES;               // K elements in one 128-byte slab
@@ -63,6 +71,14 @@ struct TileCfg {
   static constexpr int SMEM_BYTES =
       1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;             // double-buffered accumulator
+  // Cluster split-K: once the main loop is over, the pipeline stages receive the other K groups'
+  // partial accumulators of the columns this CTA finishes: (KC-1) x 128 rows x BN/KC columns x 4 B,
+  // behind the 16 KB the tail-helper warps stage their stores in.
+  static constexpr int XCHG_SLICES = BN / KC / 32;     // 32-column accumulator slices per K group
+  static constexpr int XCHG_OFF = 4 * EPI_BUFS * EPI_BUF_BYTES;
+  static constexpr int XCHG_BYTES = (KC - 1) * BM * (BN / KC) * 4;
+  static_assert(KC == 1 || (CTAS == 2 && BN == 256), "cluster split-K is built for paired 256-column tiles");
+  static_assert(KC == 1 || XCHG_OFF + XCHG_BYTES <= STAGES * STAGE_BYTES, "exchange buffer exceeds the stages");
   static_assert(NGRP >= 1, "B tile narrower than one 128-byte column group");
   static_assert(TMEM_COLS == 256 || TMEM_COLS == 512 || TMEM_COLS == 128, "TMEM columns");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
@@ -197,20 +213,42 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Loads 32 consecutive elements of row `row` of a full [M,N] operand, starting at column col0,
-// as floats.  Columns >= ncols_total read as 0.
-__device__ __forceinline__ void load_mat_row32(const MatArg& m, int l, int row, int col0,
-                                               int ncols_total, float (&out)[32]) {
+// Reading 32 consecutive elements of row `row` of a full [M,N] operand (residual, cos_sin) as floats,
+// in two phases so the loads can be in flight while the accumulator is read out of TMEM.
+// Phase 1 issues the 16-byte loads into raw words (bf16 uses raw[0..3], fp32 raw[0..7]) and returns
+//   1: loads issued   2: ragged or unaligned, phase 2 reads element by element.
+__device__ __forceinline__ int mat_row32_issue(const MatArg& m, int l, int row, int col0,
+                                               int ncols_total, uint4 (&raw)[8]) {
   const long long off = static_cast<long long>(l) * m.batch_stride +
                         static_cast<long long>(row) * m.ld + col0;
   if (m.dtype == DT_BF16) {
     const __nv_bfloat16* ptr = reinterpret_cast<const __nv_bfloat16*>(m.ptr) + off;
     if (col0 + 32 <= ncols_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
-      const uint4* p4 = reinterpret_cast<const uint4*>(ptr);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) raw[j] = __ldg(reinterpret_cast<const uint4*>(ptr) + j);
+      return 1;
+    }
+    return 2;
+  }
+  const float* ptr = reinterpret_cast<const float*>(m.ptr) + off;
+  if (col0 + 32 <= ncols_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) raw[j] = __ldg(reinterpret_cast<const uint4*>(ptr) + j);
+    return 1;
+  }
+  return 2;
+}
+
+// Phase 2: decodes the raw words (mode 1) or reads the elements one by one (mode 2).  Columns >=
+// ncols_total read as 0.
+__device__ __forceinline__ void mat_row32_finish(int mode, const uint4 (&raw)[8], const MatArg& m,
+                                                 int l, int row, int col0, int ncols_total,
+                                                 float (&out)[32]) {
+  if (mode == 1) {
+    if (m.dtype == DT_BF16) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        uint4 u = __ldg(p4 + j);
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           out[j * 8 + t * 2 + 0] = __uint_as_float(w[t] << 16);
@@ -219,22 +257,69 @@ __device__ __forceinline__ void load_mat_row32(const MatArg& m, int l, int row, 
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        out[i] = (col0 + i < ncols_total) ? __bfloat162float(ptr[i]) : 0.0f;
+      for (int j = 0; j < 8; ++j) {
+        out[j * 4 + 0] = __uint_as_float(raw[j].x); out[j * 4 + 1] = __uint_as_float(raw[j].y);
+        out[j * 4 + 2] = __uint_as_float(raw[j].z); out[j * 4 + 3] = __uint_as_float(raw[j].w);
+      }
     }
+    return;
+  }
+  const long long off = static_cast<long long>(l) * m.batch_stride +
+                        static_cast<long long>(row) * m.ld + col0;
+  if (m.dtype == DT_BF16) {
+    const __nv_bfloat16* ptr = reinterpret_cast<const __nv_bfloat16*>(m.ptr) + off;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      out[i] = (col0 + i < ncols_total) ? __bfloat162float(ptr[i]) : 0.0f;
   } else {
     const float* ptr = reinterpret_cast<const float*>(m.ptr) + off;
-    if (col0 + 32 <= ncols_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
-      const float4* p4 = reinterpret_cast<const float4*>(ptr);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float4 f = __ldg(p4 + j);
-        out[j * 4 + 0] = f.x; out[j * 4 + 1] = f.y; out[j * 4 + 2] = f.z; out[j * 4 + 3] = f.w;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) out[i] = (col0 + i < ncols_total) ? ptr[i] : 0.0f;
-    }
+    for (int i = 0; i < 32; ++i) out[i] = (col0 + i < ncols_total) ? ptr[i] : 0.0f;
+  }
+}
+
+__device__ __forceinline__ void load_mat_row32(const MatArg& m, int l, int row, int col0,
+                                               int ncols_total, float (&out)[32]) {
+  uint4 raw[8];
+  const int mode = mat_row32_issue(m, l, row, col0, ncols_total, raw);
+  mat_row32_finish(mode, raw, m, l, row, col0, ncols_total, out);
+}
+
+// Column of the cos_sin operand that output column gcol reads, and the operand's width.
+__device__ __forceinline__ int cos_sin_col(const EpiParams& e, int gcol) {
+  return e.cos_sin_period > 0 ? (gcol % e.cos_sin_period) : gcol;
+}
+__device__ __forceinline__ int cos_sin_width(const EpiParams& e, int N) {
+  return e.cos_sin_period > 0 ? e.cos_sin_period : N;
+}
+
+// Which full-matrix operand of the flat program is fetched ahead of the accumulator read.
+enum : int { PRE_NONE = 0, PRE_RESIDUAL = 1, PRE_COS_SIN = 2 };
+__device__ __forceinline__ int preload_choice(const EpiParams& e) {
+  return e.pair == PAIR_ROPE ? PRE_COS_SIN : (e.residual.enabled ? PRE_RESIDUAL : PRE_NONE);
+}
+
+// Asks L2 for this row's part of the full-matrix operands of tile columns [n0, n0 + ncols): issued
+// by the epilogue warps while the tile's main loop still runs, so the operand reads of the epilogue
+// proper hit L2 instead of waiting for HBM.  `part` of `nparts` warps that share the row.
+__device__ __forceinline__ void prefetch_tile_operands(const EpiParams& e, int N, int l, int row,
+                                                       int n0, int ncols, int part, int nparts) {
+  if (e.residual.enabled) {
+    const int es = e.residual.dtype == DT_BF16 ? 2 : 4;
+    const char* base = reinterpret_cast<const char*>(e.residual.ptr) +
+                       (static_cast<long long>(l) * e.residual.batch_stride +
+                        static_cast<long long>(row) * e.residual.ld + n0) * es;
+    for (int off = part * 128; off < ncols * es; off += nparts * 128) ptx::prefetch_l2(base + off);
+  }
+  if (e.pair == PAIR_ROPE) {
+    const int width = cos_sin_width(e, N);
+    int c0 = cos_sin_col(e, n0), nc = ncols;
+    if (nc >= width) { c0 = 0; nc = width; }          // the tile walks the whole per-head table
+    if (c0 + nc > width) nc = width - c0;
+    const char* base = reinterpret_cast<const char*>(e.cos_sin.ptr) +
+                       (static_cast<long long>(l) * e.cos_sin.batch_stride +
+                        static_cast<long long>(row) * e.cos_sin.ld + c0) * 4;
+    for (int off = part * 128; off < nc * 4; off += nparts * 128) ptx::prefetch_l2(base + off);
   }
 }
 
@@ -259,18 +344,22 @@ __device__ __forceinline__ void store_bf16_row(__nv_bfloat16* ptr, const uint32_
 // Runs the flat epilogue program on 32 accumulator columns of one row.
 //   r      raw TMEM words (fp32 bits or int32)
 //   v      results; for the compact layout only v[0..15] are meaningful (one per pair)
-//   gcol0  global column of r[0];  tcol0 column inside the CTA tile (index into cvec/bvec)
+//   gcol0  global column of r[0]
+//   pre_which / pre_mode / pre   the full-matrix operand whose loads were issued ahead of the
+//          accumulator read (mat_row32_issue), if any; the other one is loaded here
 template <int KIND>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const uint32_t (&r)[32],
                                                float (&v)[32], int row, bool row_ok, int l,
-                                               int gcol0, float rs) {
+                                               int gcol0, float rs, int pre_which, int pre_mode,
+                                               const uint4 (&pre)[8]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i)
     v[i] = (KIND == 0) ? __uint_as_float(r[i]) : static_cast<float>(static_cast<int>(r[i]));
 
   if (e.residual.enabled && row_ok) {
     float t[32];
-    load_mat_row32(e.residual, l, row, gcol0, N, t);
+    if (pre_which == PRE_RESIDUAL) mat_row32_finish(pre_mode, pre, e.residual, l, row, gcol0, N, t);
+    else load_mat_row32(e.residual, l, row, gcol0, N, t);
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] += t[i];
   }
@@ -337,9 +426,10 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
   } else if (e.pair == PAIR_ROPE) {
     float cs[32];
     if (row_ok) {
-      const int ccol = e.cos_sin_period > 0 ? (gcol0 % e.cos_sin_period) : gcol0;
-      const int climit = e.cos_sin_period > 0 ? e.cos_sin_period : N;
-      load_mat_row32(e.cos_sin, l, row, ccol, climit, cs);
+      const int ccol = cos_sin_col(e, gcol0);
+      const int climit = cos_sin_width(e, N);
+      if (pre_which == PRE_COS_SIN) mat_row32_finish(pre_mode, pre, e.cos_sin, l, row, ccol, climit, cs);
+      else load_mat_row32(e.cos_sin, l, row, ccol, climit, cs);
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i) cs[i] = 0.0f;
@@ -361,11 +451,12 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
   }
 }
 
-template <int KIND, int BN, int CTAS, int KS>
+template <int KIND, int BN, int CTAS, int KS, int KC>
 __global__ void __launch_bounds__(384, 1)
 gemm_evt_kernel(const __grid_constant__ GemmParams p) {
-  using C = TileCfg<KIND, BN, CTAS, KS>;
+  using C = TileCfg<KIND, BN, CTAS, KS, KC>;
   constexpr int STAGES = C::STAGES;
+  constexpr int CLUSTER = C::CLUSTER;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -380,12 +471,20 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]    accumulator buffer drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   uint64_t* tail_bar = bars + 2 * STAGES + 6;    // [1]        the CTA's last accumulator is complete
+  uint64_t* xfree_bar = bars + 2 * STAGES + 7;   // [1]  KC>1: the other K groups' stages are idle
+  uint64_t* xdata_bar = bars + 2 * STAGES + 8;   // [1]  KC>1: their partial accumulators have landed
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint32_t cta_rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
-  const int cluster_idx = (CTAS == 2) ? static_cast<int>(ptx::cluster_id_x()) : blockIdx.x;
-  const int num_clusters = (CTAS == 2) ? static_cast<int>(ptx::num_clusters_x()) : gridDim.x;
+  // Rank inside the cluster = K group * CTAS + rank inside the MMA pair (cta_group::2 pairs the two
+  // CTAs whose cluster ranks differ in the last bit).
+  const uint32_t cluster_rank = (CLUSTER > 1) ? ptx::cluster_ctarank() : 0u;
+  const uint32_t cta_rank = cluster_rank & static_cast<uint32_t>(CTAS - 1);
+  const uint32_t kc = cluster_rank / CTAS;            // this pair's K group, 0 when KC == 1
+  const uint32_t pair_base = kc * CTAS;               // cluster rank of this pair's leader
+  const int cluster_idx = (CLUSTER > 1) ? static_cast<int>(ptx::cluster_id_x()) : blockIdx.x;
+  const int num_clusters = (CLUSTER > 1) ? static_cast<int>(ptx::num_clusters_x()) : gridDim.x;
+  const int xchg_warps = (p.diag & 16) ? C::EPI_WARPS : C::EPI_WARPS + 4;   // warps in the exchange
   const int total_items = p.total_items;
   const long long budget = p.wait_budget;
 
@@ -401,7 +500,11 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(ptx::smem_u32(&tfull_bar[b]), 1);
-      if (b == 0) ptx::mbar_init(ptx::smem_u32(tail_bar), 1);
+      if (b == 0) {
+        ptx::mbar_init(ptx::smem_u32(tail_bar), 1);
+        ptx::mbar_init(ptx::smem_u32(xfree_bar), KC > 1 ? KC - 1 : 1);
+        ptx::mbar_init(ptx::smem_u32(xdata_bar), KC > 1 ? (KC - 1) * xchg_warps * 32 : 1);
+      }
       ptx::mbar_init(ptx::smem_u32(&tempty_bar[b]), C::EPI_WARPS * CTAS);
     }
     ptx::fence_mbar_init();
@@ -412,7 +515,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if constexpr (CTAS == 2) {
+  if constexpr (CLUSTER > 1) {
     ptx::cluster_arrive();
     ptx::cluster_wait();
   }
@@ -434,6 +537,10 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t pol_a = p.l2_hint_a == 1 ? ptx::l2_policy_evict_last()
+                                              : (p.l2_hint_a == 2 ? ptx::l2_policy_evict_first() : 0ull);
+      const uint64_t pol_b = p.l2_hint_b == 1 ? ptx::l2_policy_evict_last()
+                                              : (p.l2_hint_b == 2 ? ptx::l2_policy_evict_first() : 0ull);
       for (int w = cluster_idx; w < total_items && ok; w += num_clusters) {
         const WorkItem wi = decode_item(p, schedule_item(p, w, cluster_idx, num_clusters));
         const TileCoord tc = decode_tile(p, wi.tile);
@@ -441,14 +548,17 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         const int col0 = tc.tn * BN + static_cast<int>(cta_rank) * C::BN_CTA;
         const int la = p.a_batched ? tc.l : 0;
         const int lb = p.b_batched ? tc.l : 0;
-        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
+        // cluster split-K: this pair takes the kc-th of KC equal parts of the item's K range
+        const int kb_lo = (KC > 1) ? wi.kb0 + static_cast<int>(kc) * (wi.kb1 - wi.kb0) / KC : wi.kb0;
+        const int kb_hi = (KC > 1) ? wi.kb0 + static_cast<int>(kc + 1) * (wi.kb1 - wi.kb0) / KC : wi.kb1;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, budget)) {
             if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_PRODUCER_EMPTY);
             ok = false;
             break;
           }
           const uint32_t my_full = ptx::smem_u32(&full_bar[stage]);
-          const uint32_t full_addr = (CTAS == 2) ? ptx::mapa(my_full, 0) : my_full;
+          const uint32_t full_addr = (CTAS == 2) ? ptx::mapa(my_full, pair_base) : my_full;
           if (p.diag & 1) {  // diagnostics: no operand traffic, the stage is "full" at once
             if (cta_rank == 0) ptx::mbar_arrive(my_full);
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -464,15 +574,25 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
               a2 = ka / p.a_k_slab;
               ka -= a2 * p.a_k_slab;
             }
-            ptx::tma_load_3d<CTAS>(ptx::smem_u32(sa + ks * C::A_SLAB_BYTES), &p.tm_a, full_addr, ka,
-                                   row0, a2);
+            if (p.l2_hint_a)
+              ptx::tma_load_3d_hint<CTAS>(ptx::smem_u32(sa + ks * C::A_SLAB_BYTES), &p.tm_a, full_addr, ka,
+                                          row0, a2, pol_a);
+            else
+              ptx::tma_load_3d<CTAS>(ptx::smem_u32(sa + ks * C::A_SLAB_BYTES), &p.tm_a, full_addr, ka,
+                                     row0, a2);
           }
 #pragma unroll
-          for (int g = 0; g < C::NGRP; ++g)
-            ptx::tma_load_3d<CTAS>(ptx::smem_u32(sb + g * C::GRP_BYTES), &p.tm_b, full_addr,
-                                   col0 + g * C::GRP_COLS, kb * C::KBLK, lb);
+          for (int g = 0; g < C::NGRP; ++g) {
+            if (p.l2_hint_b)
+              ptx::tma_load_3d_hint<CTAS>(ptx::smem_u32(sb + g * C::GRP_BYTES), &p.tm_b, full_addr,
+                                          col0 + g * C::GRP_COLS, kb * C::KBLK, lb, pol_b);
+            else
+              ptx::tma_load_3d<CTAS>(ptx::smem_u32(sb + g * C::GRP_BYTES), &p.tm_b, full_addr,
+                                     col0 + g * C::GRP_COLS, kb * C::KBLK, lb);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
+        if constexpr (KC > 1) break;   // one tile per cluster: the stages become the exchange buffer
       }
     }
   } else if (warp == 1) {
@@ -492,7 +612,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
-        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
+        const int kb_lo = (KC > 1) ? wi.kb0 + static_cast<int>(kc) * (wi.kb1 - wi.kb0) / KC : wi.kb0;
+        const int kb_hi = (KC > 1) ? wi.kb0 + static_cast<int>(kc + 1) * (wi.kb1 - wi.kb0) / KC : wi.kb1;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, budget)) {
             if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_MMA_FULL);
             ok = false;
@@ -512,22 +634,23 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             const int a_off = (k / MMAS_PER_SLAB) * C::A_SLAB_BYTES + (k % MMAS_PER_SLAB) * 32;
             ptx::umma<KIND, CTAS>(d_tmem, adesc + static_cast<uint64_t>(a_off >> 4),
                                   bdesc + static_cast<uint64_t>(k * ((C::UK * 128) >> 4)), idesc,
-                                  (kb > wi.kb0 || k > 0) ? 1u : 0u);
+                                  (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           const uint32_t eb = ptx::smem_u32(&empty_bar[stage]);
           ptx::umma_commit<CTAS>(eb);
-          if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(eb, 1));
+          if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(eb, pair_base + 1));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         const uint32_t tb = ptx::smem_u32(&tfull_bar[buf]);
         ptx::umma_commit<CTAS>(tb);
-        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(tb, 1));
-        if (w + num_clusters >= total_items) {   // last item: also wake the warps that help with it
+        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(tb, pair_base + 1));
+        if (w + num_clusters >= total_items || KC > 1) {   // last item: also wake the warps that help with it
           const uint32_t lb = ptx::smem_u32(tail_bar);
           ptx::umma_commit<CTAS>(lb);
-          if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(lb, 1));
+          if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(lb, pair_base + 1));
         }
+        if constexpr (KC > 1) break;
       }
     }
   }
@@ -552,12 +675,14 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     const int n_out = compact ? (p.N >> 1) : p.N;
     const int slices_per_unit = compact ? 2 : 1;   // 32 output columns = 1 or 2 accumulator slices
     const uint32_t tempty_leader =
-        (CTAS == 2) ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0) : ptx::smem_u32(&tempty_bar[0]);
+        (CTAS == 2) ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), pair_base) : ptx::smem_u32(&tempty_bar[0]);
+    const int pre_which = preload_choice(e);
     int it = 0;
     for (int w = cluster_idx; w < total_items; w += num_clusters, ++it) {
+      if (KC > 1 && it > 0) break;   // cluster split-K: one tile per cluster
       const WorkItem wi = decode_item(p, schedule_item(p, w, cluster_idx, num_clusters));
       // the CTA's last item, if it is a whole tile, is shared three ways per quadrant
-      const bool shared3 = (w + num_clusters >= total_items) && wi.split_idx < 0 && !(p.diag & 16);
+      const bool shared3 = (w + num_clusters >= total_items || KC > 1) && wi.split_idx < 0 && !(p.diag & 16);
       const TileCoord tc = decode_tile(p, wi.tile);
       const int buf = it & 1;
       const int m0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
@@ -568,6 +693,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       float rs = 1.0f;
       if (e.row_scale.enabled && row_ok && (!helper || shared3))
         rs = load_vec_elem(e.row_scale, static_cast<long long>(l) * e.row_scale.batch_stride + row);
+      // while the tile's main loop runs: bring this row's residual / cos_sin lines into L2
+      if (!helper && row_ok && pre_which != PRE_NONE && p.d_dtype != DT_S32)
+        prefetch_tile_operands(e, p.N, l, row, n0, min(BN, p.N - n0), half, 2);
 
       // Helpers wait on a barrier of their own that completes once, with the CTA's last
       // accumulator: the two-phase barriers of the accumulator buffers name a phase by one parity
@@ -655,9 +783,61 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
                     static_cast<size_t>(q * 32 + lane) * 4;
       }
 
-      for (int u = u_first; u < nunits; u += u_step) {
+      // Cluster split-K.  Every CTA of the cluster holds, for its 128 rows, the partial accumulator of
+      // its pair's K range over all BN columns.  K group g finishes columns [g*BN/KC, (g+1)*BN/KC):
+      // each CTA sends the other groups' columns of its partial to the CTA with the same rows in that
+      // group (st.shared::cluster into its idle pipeline stages) and receives KC-1 partials of its own
+      // columns, which the unit loop below adds, in group order, to what it reads from TMEM.
+      int u_end = nunits;
+      const uint4* xrecv = nullptr;
+      if constexpr (KC > 1) {
+        constexpr int SPG = C::XCHG_SLICES;
+        const uint32_t xfree = ptx::smem_u32(xfree_bar), xdata = ptx::smem_u32(xdata_bar);
+        const uint32_t xbuf = ptx::smem_u32(stage_base + C::XCHG_OFF);
+        const int workers = shared3 ? 3 : 2;
+        bool ok = true;
+        // this CTA's MMAs are done (the accumulator barrier has completed): its stages are idle
+        if (warp == 4 && lane == 0) {
+#pragma unroll
+          for (int g = 0; g < KC; ++g)
+            if (g != static_cast<int>(kc)) ptx::mbar_arrive_cluster(ptx::mapa(xfree, g * CTAS + cta_rank));
+        }
+        if (!ptx::mbar_wait_cluster(xfree, 0u, budget)) ok = false;
+        if (ok) {
+          for (int idx = half; idx < (KC - 1) * SPG; idx += workers) {
+            const int gslot = idx / SPG, sl = idx - gslot * SPG;
+            const int g = gslot < static_cast<int>(kc) ? gslot : gslot + 1;      // destination K group
+            const int slot = static_cast<int>(kc) < g ? static_cast<int>(kc) : static_cast<int>(kc) - 1;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(g * (BN / KC) + sl * 32), r);
+            ptx::tmem_ld_wait();
+            // receiver layout [sender slot][slice][16-byte chunk][row]: a warp's store is 512 contiguous bytes
+            const uint32_t dst = ptx::mapa(xbuf, g * CTAS + cta_rank) +
+                                 static_cast<uint32_t>((((slot * SPG + sl) * 8) * C::BM + q * 32 + lane) * 16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              ptx::st_shared_cluster_v4(dst + static_cast<uint32_t>(j * C::BM * 16),
+                                        make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+          }
+        }
+        // every thread releases its own stores to every other group, then waits for theirs
+#pragma unroll
+        for (int g = 0; g < KC; ++g)
+          if (g != static_cast<int>(kc)) ptx::mbar_arrive_cluster(ptx::mapa(xdata, g * CTAS + cta_rank));
+        if (ok && !ptx::mbar_wait_cluster(xdata, 0u, budget)) ok = false;
+        if (!ok) {
+          if (p.status && lane == 0) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_CLUSTER_EXCHANGE);
+          break;
+        }
+        const int upg = SPG / slices_per_unit;                  // output units per K group
+        u_first = static_cast<int>(kc) * upg + half;
+        u_end = min(nunits, (static_cast<int>(kc) + 1) * upg);
+        xrecv = reinterpret_cast<const uint4*>(stage_base + C::XCHG_OFF) + (q * 32 + lane);
+      }
+
+      for (int u = u_first; u < u_end; u += u_step) {
         uint32_t pk[16];
-        const bool last_unit = (u + u_step >= nunits);
+        const bool last_unit = (u + u_step >= u_end);
         int out_col0 = 0;
         bool stored_direct = false;
 #pragma unroll 1
@@ -667,10 +847,39 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           float v[32];
           uint32_t r[32];
           const int tcol0 = s * 32;
+          // the residual / cos_sin loads of this slice go out before the accumulator is read
+          uint4 pre[8];
+          int pre_mode = 0;
+          if (row_ok && !(p.diag & 4) && p.d_dtype != DT_S32) {
+            if (pre_which == PRE_RESIDUAL)
+              pre_mode = mat_row32_issue(e.residual, l, row, n0 + tcol0, p.N, pre);
+            else if (pre_which == PRE_COS_SIN)
+              pre_mode = mat_row32_issue(e.cos_sin, l, row, cos_sin_col(e, n0 + tcol0), cos_sin_width(e, p.N), pre);
+          }
           if (part_base == nullptr) {
             ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
             ptx::tmem_ld_wait();
             if (last_unit && (h + 1 == slices_per_unit || s + 1 >= nsub)) release_tmem();
+            if constexpr (KC > 1) {
+              // add the other K groups' partials of this slice, in group order
+              const int sl = s - static_cast<int>(kc) * C::XCHG_SLICES;
+#pragma unroll
+              for (int slot = 0; slot < KC - 1; ++slot) {
+                const uint4* src = xrecv + static_cast<size_t>((slot * C::XCHG_SLICES + sl) * 8) * C::BM;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const uint4 x = src[j * C::BM];
+                  const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                  for (int t = 0; t < 4; ++t) {
+                    if constexpr (KIND == 0)
+                      r[4 * j + t] = __float_as_uint(__uint_as_float(r[4 * j + t]) + __uint_as_float(xs[t]));
+                    else
+                      r[4 * j + t] = static_cast<uint32_t>(static_cast<int>(r[4 * j + t]) + static_cast<int>(xs[t]));
+                  }
+                }
+              }
+            }
           } else {
             // sum the slices in slice order (the same order whichever slice arrived last); L2 loads:
             // the partials were written by other SMs
@@ -728,7 +937,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             stored_direct = true;
             continue;
           }
-          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs);
+          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs, pre_which, pre_mode, pre);
           if (e.row_sumsq != nullptr) {
             // side output for a following RMSNorm: this row's sum of squares over these 32 columns
             const int nv = p.N - (n0 + tcol0);
@@ -834,7 +1043,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   // ------------------------------------------------------------------ teardown
   ptx::tc_fence_before();
   __syncthreads();
-  if constexpr (CTAS == 2) {
+  if constexpr (CLUSTER > 1) {   // no CTA leaves while a peer may still write its barriers or stages
     ptx::cluster_arrive();
     ptx::cluster_wait();
   }

@@ -87,6 +87,12 @@ __global__ void __launch_bounds__(1024) ref_gemm_kernel(const TA* A, long long l
 
 __device__ unsigned long long g_mismatches;
 __device__ unsigned long long g_first_mismatch;
+// the first kListMax disagreements found (in no particular order), for the verbose listing
+static const int kListMax = 64;
+__device__ unsigned int g_list_count;
+__device__ unsigned long long g_list_index[kListMax];
+__device__ float g_list_a[kListMax];
+__device__ float g_list_b[kListMax];
 
 template <class T>
 __global__ void compare_kernel(const T* a, const T* b, long long n, float eps, float floor_) {
@@ -104,6 +110,12 @@ __global__ void compare_kernel(const T* a, const T* b, long long n, float eps, f
     if (!ok) {
       ++local;
       atomicMin(&g_first_mismatch, static_cast<unsigned long long>(i));
+      const unsigned int slot = atomicAdd(&g_list_count, 1u);
+      if (slot < kListMax) {
+        g_list_index[slot] = static_cast<unsigned long long>(i);
+        g_list_a[slot] = x;
+        g_list_b[slot] = y;
+      }
     }
   }
   if (local) atomicAdd(&g_mismatches, local);
@@ -184,6 +196,9 @@ xf_status xf_harness_compare(int dtype, const void* a, const void* b, long long 
   cudaError_t e = cudaMemcpyToSymbolAsync(g_mismatches, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st);
   if (e == cudaSuccess)
     e = cudaMemcpyToSymbolAsync(g_first_mismatch, &none, sizeof(none), 0, cudaMemcpyHostToDevice, st);
+  unsigned int zero32 = 0;
+  if (e == cudaSuccess)
+    e = cudaMemcpyToSymbolAsync(g_list_count, &zero32, sizeof(zero32), 0, cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) { xf::set_error("compare: %s", cudaGetErrorString(e)); return XF_ERR_INTERNAL; }
   if (n > 0) {
     switch (dtype) {
@@ -200,19 +215,25 @@ xf_status xf_harness_compare(int dtype, const void* a, const void* b, long long 
   if (e != cudaSuccess) { xf::set_error("compare: %s", cudaGetErrorString(e)); return XF_ERR_INTERNAL; }
   *mismatches = static_cast<long long>(out);
   if (out != 0 && getenv("XF_HARNESS_VERBOSE")) {
-    // diagnostic for harness runs: where the first disagreement is and what the two values are
-    unsigned long long first = 0;
-    cudaMemcpyFromSymbol(&first, g_first_mismatch, sizeof(first));
-    float va = 0.f, vb = 0.f;
-    const size_t es = (dtype == XF_DT_BF16) ? 2 : (dtype == XF_DT_S8 ? 1 : 4);
-    unsigned char ra[4] = {0, 0, 0, 0}, rb[4] = {0, 0, 0, 0};
-    cudaMemcpy(ra, static_cast<const unsigned char*>(a) + first * es, es, cudaMemcpyDefault);
-    cudaMemcpy(rb, static_cast<const unsigned char*>(b) + first * es, es, cudaMemcpyDefault);
-    if (dtype == XF_DT_BF16) {
-      unsigned int ua = (unsigned int)(ra[0] | (ra[1] << 8)) << 16, ub = (unsigned int)(rb[0] | (rb[1] << 8)) << 16;
-      memcpy(&va, &ua, 4); memcpy(&vb, &ub, 4);
-    } else if (dtype == XF_DT_F32) { memcpy(&va, ra, 4); memcpy(&vb, rb, 4); }
-    fprintf(stderr, "compare: %llu of %lld elements differ; first at index %llu: %g vs %g\n", out, n, first, va, vb);
+    // diagnostic for harness runs: which elements disagree and what the two values are
+    // (XF_HARNESS_VERBOSE=1; up to 64 of them, sorted by index)
+    unsigned int cnt = 0;
+    static unsigned long long idx[kListMax];
+    static float va[kListMax], vb[kListMax];
+    cudaMemcpyFromSymbol(&cnt, g_list_count, sizeof(cnt));
+    cudaMemcpyFromSymbol(idx, g_list_index, sizeof(idx));
+    cudaMemcpyFromSymbol(va, g_list_a, sizeof(va));
+    cudaMemcpyFromSymbol(vb, g_list_b, sizeof(vb));
+    if (cnt > (unsigned int)kListMax) cnt = kListMax;
+    fprintf(stderr, "compare: %llu of %lld elements differ (eps %g, floor %g)\n", out, n, epsilon, nonzero_floor);
+    for (unsigned int i = 0; i < cnt; ++i) {   // selection sort: at most 64 entries
+      unsigned int m = i;
+      for (unsigned int j = i + 1; j < cnt; ++j) if (idx[j] < idx[m]) m = j;
+      unsigned long long ti = idx[i]; idx[i] = idx[m]; idx[m] = ti;
+      float ta = va[i]; va[i] = va[m]; va[m] = ta;
+      float tb = vb[i]; vb[i] = vb[m]; vb[m] = tb;
+      fprintf(stderr, "  [%llu] expected %.9g got %.9g\n", idx[i], va[i], vb[i]);
+    }
   }
   return XF_SUCCESS;
 }

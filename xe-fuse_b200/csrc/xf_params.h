@@ -18,6 +18,7 @@ enum : int {
   DEV_TIMEOUT_MMA_TMEM_EMPTY = 3,
   DEV_TIMEOUT_EPI_TMEM_FULL = 4,
   DEV_TIMEOUT_SPLIT_PARTIALS = 5,   // a K slice never saw the other slices' partial accumulators
+  DEV_TIMEOUT_CLUSTER_EXCHANGE = 6, // cluster split-K: the other K groups' partials never arrived
 };
 
 struct VecArg {
@@ -62,6 +63,7 @@ struct alignas(64) GemmParams {
   int group_m;             // rasterisation group height in cluster tiles
   int a_batched, b_batched;  // 0: batch stride 0, always use batch coordinate 0
   int a_k_slab;            // >0: A is stored as K slabs of this many elements (third tensor-map mode)
+  int l2_hint_a, l2_hint_b;  // L2 policy of the A / B loads: 0 default, 1 evict last, 2 evict first
   void* D;
   void* D_peer[7];         // further destinations of the same output (peer-mapped memory)
   int num_d_peer;          // 0..7
