@@ -52,6 +52,7 @@ WORKLOADS = {
     "k4v2_q": [("k4v2", 4096, 4096, 4096, "bf16")],
     "k4v2_kv": [("k4v2", 4096, 1024, 4096, "bf16")],
     "w8a8": [("w8a8", 8192, 8192, 28672, "s8")],
+    "k0a": [("k0a", 8192, 8192, 8192, "bf16")],          # the O-projection stage of the chain, alone
     # Llama-3-70B decoder-layer GEMM chain, M = 8192 tokens
     "pipeline": [("k4v2", 8192, 10240, 8192, "bf16"), ("k0a", 8192, 8192, 8192, "bf16"),
                  ("k2", 8192, 57344, 8192, "bf16"), ("k0a", 8192, 8192, 28672, "bf16", "chain")],
@@ -62,6 +63,8 @@ DESCR = {
     "k4v2_q": "k4v2 GEMM+RMSNorm+RoPE Llama-3-8B Q-proj M=4096 K=4096 N=4096, table [4096,128] theta=5e5",
     "k4v2_kv": "k4v2 GEMM+RMSNorm+RoPE Llama-3-8B K-proj M=4096 K=4096 N=1024, table [4096,128] theta=5e5",
     "w8a8": "w8a8_dequant_biased Llama-3-70B FFN down M=8192 K=28672 N=8192 int8 -> bf16, bf16 bias",
+    "k0a": "k0a GEMM+residual+gamma Llama-3-70B O-proj M=8192 K=8192 N=8192 bf16, residual bf16 [8192,8192]",
+    "rstd_quant": "RMSNorm + per-token int8 quantisation producer (compute_rstd_and_quantize) over bf16 [8192,8192]",
     "pipeline": "Llama-3-70B layer GEMM chain M=8192: QKV k4v2 (K=8192,N=10240), O k0a (8192,8192), "
                 "gate/up k2 (K=8192,N=57344), down k0a (K=28672,N=8192)",
 }
@@ -218,7 +221,8 @@ def gen_stage(stage, rank, world, seed, dev, host_x=True):
     return h
 
 
-def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=None, consume=None):
+def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=None, consume=None,
+                    x_buffer=None):
     """Device buffers + the fused plan of one stage.  With `share` (an earlier build of the same
     stage) the static operands (weights, per-column vectors, tables) are reused and only the
     per-step buffers (activations, row scales, output) are new."""
@@ -241,6 +245,10 @@ def build_stage_gpu(capi, stage, h, dev, share=None, prev=None, world=1, gather=
             s["gather_from"] = prev["D"]
             a_k_slabs = True
         s["R"] = None
+    elif x_buffer is not None:         # activations live in a buffer the caller provides (peer-mapped)
+        s["X"] = x_buffer
+        s["X"].copy_(h["X"], non_blocking=True)
+        s["R"] = h["R"].to(dev, non_blocking=True)
     else:
         s["X"] = h["X"].to(dev, non_blocking=True) if h["X"].device != dev or share else h["X"]
         s["R"] = h["R"].to(dev, non_blocking=True) if h["R"].device != dev or share else h["R"]
@@ -361,7 +369,7 @@ class Workload:
         self.flops_total = self.flops_rank * self.world
         self.turn = 0
 
-    def build_set(self, share_from=None, fresh_weights=False):
+    def build_set(self, share_from=None, fresh_weights=False, x_alloc=None):
         """One set of per-step buffers + plans for all stages.  When a stage feeds a chained
         consumer on several GPUs, its output goes to a symmetric gathered buffer: fused into the
         producer's epilogue (gather == "fused") or by ncclAllGather afterwards ("nccl")."""
@@ -377,9 +385,10 @@ class Workload:
             if nxt_chain and self.world > 1 and self.gather == "fused":
                 n_out = (st[2] // self.world) // (2 if st[0] == "k2" else 1)
                 gather = xf.sharding.GatherBuffer(dist, st[1], n_out, torch.bfloat16, dev)
+            xb = x_alloc(h["X"]) if (x_alloc is not None and len(st) <= 5) else None
             out.append(build_stage_gpu(capi, st, h, dev, share=share_from[i] if share_from else None,
                                        prev=out[-1] if out else None, world=self.world, gather=gather,
-                                       consume=pending))
+                                       consume=pending, x_buffer=xb))
             pending = gather
         return out
 
@@ -441,39 +450,74 @@ class Workload:
     # row scales from pinned host memory and reads its whole output back.  Two device buffer sets
     # and three streams (copy-in, compute, copy-out) let step i+1's upload and step i-1's read-back
     # overlap step i's kernels, as a serving loop would; weights stay resident.
-    def e2e(self, steps):
+    def e2e(self, steps, exchange="copy"):
         torch, ctx = self.torch, self.ctx
         dev, dist, world, rank = ctx["dev"], ctx["dist"], self.world, ctx["rank"]
-        gpu = self.gpu
-        gpu2 = self.build_set(share_from=gpu)
-        sets = [gpu, gpu2]
+        # From 4 ranks up the replicated activations are uploaded in row shards (each rank 1/N of
+        # the rows over its own PCIe link) and exchanged over NVLink: at 2 ranks the read-back of
+        # the output is the longer PCIe transfer either way.
+        shard_upload = world >= 4 and all(len(st) > 5 or st[1] % world == 0 for st in self.stages)
+        peer_push = shard_upload and exchange == "copy"
+        handles = []
+
+        def sym_alloc(like):           # activations in symmetric (peer-mapped) memory
+            import torch.distributed._symmetric_memory as symm
+            t = symm.empty(tuple(like.shape), dtype=like.dtype, device=dev)
+            hdl = symm.rendezvous(t, group=dist.group.WORLD)
+            handles.append((t, hdl))
+            return t
+
+        if peer_push:
+            sets = [self.build_set(share_from=self.gpu, x_alloc=sym_alloc) for _ in range(2)]
+        else:
+            sets = [self.gpu, self.build_set(share_from=self.gpu)]
+        gpu = sets[0]
+        peers = {}                     # X buffer -> views of the same buffer on every other rank
+        for t, hdl in handles:
+            peers[t.data_ptr()] = (hdl, [hdl.get_buffer(p, tuple(t.shape), t.dtype) for p in range(world) if p != rank])
         outs = [[torch.empty(s["D"].shape, dtype=torch.bfloat16).pin_memory() for s in gpu] for _ in range(2)]
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         s_comp = torch.cuda.current_stream()
         ev_in = [torch.cuda.Event() for _ in range(2)]
         ev_k = [torch.cuda.Event() for _ in range(2)]
         ev_out = [torch.cuda.Event() for _ in range(2)]
-        # From 4 ranks up the replicated activations are uploaded in row shards and exchanged over
-        # NVLink: at 2 ranks the read-back of the output is the longer PCIe transfer either way and
-        # the gather kernel only takes SMs from the persistent GEMM.
-        shard_upload = world >= 4 and all(s["chain"] or s["X"].shape[0] % world == 0 for s in gpu)
         host = self.host
+
+        def upload(b, do_h2d=True, do_xchg=True):
+            for s, h in zip(sets[b], host):
+                if s["chain"]:
+                    continue
+                if shard_upload:
+                    m = s["X"].shape[0] // world
+                    mine = s["X"][rank * m:(rank + 1) * m]
+                    if peer_push:
+                        hdl, views = peers[s["X"].data_ptr()]
+                        if do_xchg:
+                            hdl.barrier(channel=0)      # every rank's kernels that read this set are done
+                        if do_h2d:
+                            mine.copy_(h["X"][rank * m:(rank + 1) * m], non_blocking=True)
+                        if do_xchg:
+                            # copy engines push this rank's rows into the same rows of every peer's
+                            # buffer; no SM kernel competes with the persistent GEMM
+                            for v in views:
+                                v[rank * m:(rank + 1) * m].copy_(mine, non_blocking=True)
+                            hdl.barrier(channel=1)      # all rows of the local buffer have landed
+                    else:
+                        if do_h2d:
+                            mine.copy_(h["X"][rank * m:(rank + 1) * m], non_blocking=True)
+                        if do_xchg:
+                            dist.all_gather_into_tensor(s["X"], mine)
+                elif do_h2d:
+                    s["X"].copy_(h["X"], non_blocking=True)
+                if do_h2d:
+                    s["R"].copy_(h["R"], non_blocking=True)
 
         def loop(n):
             for i in range(n):
                 b = i & 1
                 with torch.cuda.stream(s_in):
                     s_in.wait_event(ev_k[b])            # the kernels that read this buffer set are done
-                    for s, h in zip(sets[b], host):
-                        if not s["chain"]:
-                            if shard_upload:
-                                m = s["X"].shape[0] // world
-                                mine = s["X"][rank * m:(rank + 1) * m]
-                                mine.copy_(h["X"][rank * m:(rank + 1) * m], non_blocking=True)
-                                dist.all_gather_into_tensor(s["X"], mine)
-                            else:
-                                s["X"].copy_(h["X"], non_blocking=True)
-                            s["R"].copy_(h["R"], non_blocking=True)
+                    upload(b)
                     ev_in[b].record(s_in)
                 s_comp.wait_event(ev_in[b])
                 s_comp.wait_event(ev_out[b])            # the previous read-back of this output is done
@@ -487,6 +531,17 @@ class Workload:
             s_comp.wait_stream(s_in)
             s_comp.wait_stream(s_out)
 
+        def timed_on(stream, fn, n):
+            ctx["barrier"]()
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(stream):
+                a.record(stream)
+                for i in range(n):
+                    fn(i & 1)
+                z.record(stream)
+            torch.cuda.synchronize()
+            return self.max_over_ranks(a.elapsed_time(z)) / n
+
         loop(4)
         ctx["barrier"]()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -497,6 +552,13 @@ class Workload:
         ms = e0.elapsed_time(e1)
         ctx["barrier"]()
         ms = self.max_over_ranks(ms)
+        # each phase of a step alone, back to back on its own stream (max over ranks)
+        split = {"h2d": timed_on(s_in, lambda b: upload(b, do_xchg=False), steps),
+                 "kernels": timed_on(s_comp, lambda b: self.run_stages(sets[b], s_comp.cuda_stream), steps),
+                 "d2h": timed_on(s_out, lambda b: [o.copy_(s["D"], non_blocking=True)
+                                                   for s, o in zip(sets[b], outs[b])], steps)}
+        if shard_upload:
+            split["exchange"] = timed_on(s_in, lambda b: upload(b, do_h2d=False), steps)
         h2d_job = d2h_job = 0          # bytes that cross PCIe per step, all ranks together
         for s in gpu:
             d2h_job += s["d2h_bytes"] * world
@@ -505,11 +567,13 @@ class Workload:
                 h2d_job += (x_bytes if shard_upload else x_bytes * world) + (s["h2d_bytes"] - x_bytes) * world
         return {"value": self.flops_total * steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": int(h2d_job), "d2h_bytes_per_step": int(d2h_job),
-                "ms_per_step": ms / steps,
+                "ms_per_step": ms / steps, "phase_ms_alone": split,
                 "how": "double-buffered: H2D of step i+1 and D2H of step i-1 overlap the kernels of step i; "
-                       "bytes are whole-job totals over all ranks"
-                       + ("; each rank uploads 1/N of the replicated activation rows and the ranks "
-                          "all-gather them over NVLink" if shard_upload else "")}
+                       "bytes are whole-job totals over all ranks; phase_ms_alone = each phase run by itself"
+                       + ("; each rank uploads 1/N of the replicated activation rows and "
+                          + ("pushes them into every peer's buffer with copy-engine peer copies between two "
+                             "stream-ordered barriers" if peer_push else "the ranks all-gather them with NCCL")
+                          if shard_upload else "")}
 
     # ---- unfused baseline: bare GEMM + stand-alone kernel(s)
     def unfused(self, steps, fused_value):
@@ -629,6 +693,38 @@ def gather_check(ctx, steps=2):
     return "pass" if int(flag.item()) == 1 else "FAIL: fused gather differs from ncclAllGather on some rank"
 
 
+def run_rstd_quant(ctx, args, peaks):
+    """The activation-quantisation producer (kernels/compute_rstd.hpp:67-125 of the reference): one
+    HBM-bound row pass, 2 bytes read + 1 byte written per element (+ 4 per row)."""
+    torch, capi, dev = ctx["torch"], ctx["capi"], ctx["dev"]
+    M = N = 8192
+    rot = []
+    for i in range(3):      # 3 x 201 MB: every step reads cold rows
+        x = torch.randn(M, N, device=dev, generator=torch.Generator(device=dev).manual_seed(7 + i)).to(torch.bfloat16)
+        rot.append((x, torch.empty(M, N, dtype=torch.int8, device=dev), torch.empty(M, dtype=torch.float32, device=dev)))
+    turn = [0]
+
+    def step():
+        x, q, st = rot[turn[0] % len(rot)]
+        turn[0] += 1
+        capi.compute_rstd_and_quantize(x, q, st)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    ms = time_loop(torch, step, args.steps) / args.steps
+    algo = M * N * 3 + M * 4
+    gbs = algo / (ms * 1e-3) / 1e9
+    line = {"metric": "rstd+quantise producer GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16->s8", "data": "synthetic",
+            "config": {"workload": DESCR["rstd_quant"], "l2": "steps rotate over 3 inputs of 134 MB each, no flush"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm"], "traffic": None, "peak_source": f"STREAM-style copy, {peaks['src']}"},
+            "gpu_launches": args.steps}
+    print(json.dumps(line), flush=True)
+
+
 # ------------------------------------------------------------------------------ CPU arm
 def cpu_threads():
     try:
@@ -732,7 +828,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="k2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="k2", choices=sorted(WORKLOADS) + ["rstd_quant"])
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1, chained stages: all-gather fused into the producer's epilogue "
                          "(peer stores) or a separate ncclAllGather")
@@ -742,12 +838,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-unfused", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling runs)")
+    ap.add_argument("--e2e-exchange", default="copy", choices=["copy", "nccl"],
+                    help="N>=4, end-to-end arm: how the row shards of the replicated activations reach "
+                         "the other ranks: copy-engine peer copies (default) or an NCCL all-gather")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip all_configs (1 GPU) / pipeline + gather check (N > 1) and the int8 peak")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    stages = WORKLOADS[args.workload]
+    stages = WORKLOADS.get(args.workload)
+    if stages is None and (args.impl == "reference" or args.gpus > 1):
+        raise SystemExit("bench.py: the rstd_quant workload is a single-GPU row pass of this library only")
 
     if args.impl == "reference":
         run_reference_arm(args, stages)
@@ -785,6 +886,9 @@ def main():
     ctx = {"torch": torch, "xf": xf, "capi": capi, "dist": dist, "dev": dev, "world": world, "rank": rank,
            "barrier": barrier, "l2_bytes": torch.cuda.get_device_properties(dev).L2_cache_size}
 
+    if stages is None:
+        run_rstd_quant(ctx, args, peaks)
+        return
     wl = Workload(ctx, args.workload, gather=args.gather, shard_of=args.shard_of)
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     if not uuid.startswith("GPU-"):
@@ -800,7 +904,7 @@ def main():
     v_sus, ms_sus, load_window, n_sus = wl.sustained(ms_per_step, min_steps=args.steps)
     sm_sus, _ = sampler.median_sm(*load_window)
 
-    e2e = None if args.no_e2e else wl.e2e(args.steps)
+    e2e = None if args.no_e2e else wl.e2e(args.steps, exchange=args.e2e_exchange)
     unfused = None if args.no_unfused else wl.unfused(args.steps, value)
     is_s8 = stages[0][4] == "s8"
     kernels = wl.kernels()

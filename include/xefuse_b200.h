@@ -195,6 +195,9 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_NO_CLUSTER_SPLIT 65536 /* never use the cluster split-K variants (small problems: the CTA
                                     pairs of one cluster share a tile's K range and swap partial
                                     accumulators through distributed shared memory) */
+#define XF_FLAG_NO_TAIL_STAGING 262144 /* a CTA's last tile reads its residual / cos_sin operand with plain
+                                    loads like every other tile (by default TMA stages that one tile's
+                                    operand in an idle pipeline stage while the main loop drains) */
 #define XF_FLAG_FORCE_CLUSTER_SPLIT 131072 /* use a cluster split-K variant whenever K is long enough, also
                                     for problems with more tiles than co-resident clusters */
 

@@ -253,3 +253,28 @@ def test_dependent_launches_stay_ordered(flags_name, capi, oracle, cuda):
     assert np.array_equal(bf16_bits(D1), d1) or pc.compare_bf16(oracle, bf16_bits(D1), d1)[0] == 0
     assert pc.compare_bf16(oracle, bf16_bits(D2), oracle.epilogue(oracle.gemm_bf16(bf16_bits(D1), B2)))[0] == 0
     assert pc.compare_bf16(oracle, bf16_bits(D2), want)[0] == 0
+
+
+@pytest.mark.parametrize("preset,shape", [
+    ("k4v2_table", (512, 1024, 512)),      # per-head table, one tile per CTA pair
+    ("k4v2_table", (300, 640, 264)),       # ragged rows and K
+    ("k0a", (384, 768, 512)),              # residual tile
+    ("k0a", (200, 336, 208)),              # ragged: the staged tile's columns beyond N read as zero
+    ("k0_dual", (384, 768, 512)),          # residual + aux store
+    ("k0a", (2048, 4096, 512)),            # 128 paired tiles on 74 pairs: staged only for each CTA's last tile
+    ("k4v2_table", (4096, 1024, 256)),
+])
+def test_tail_operand_staging_is_bit_identical(preset, shape, capi, oracle, cuda):
+    """A CTA's last tile takes its residual / cos_sin operand from shared memory (TMA-staged while
+    the main loop drains) instead of global loads: same bits out, and inside the parity bar."""
+    M, N, K = shape
+    d = pc.make_inputs(oracle, preset, M, N, K, seed=3)
+    plan_a, got_a, aux_a = run_gpu(capi, oracle, preset, d, cuda)
+    plan_b, got_b, aux_b = run_gpu(capi, oracle, preset, d, cuda, flags=capi.FLAG_NO_TAIL_STAGING)
+    assert np.array_equal(got_a, got_b), plan_a.kernel_name
+    if aux_a is not None:
+        assert np.array_equal(aux_a, aux_b)
+    _, want = pc.expected(oracle, preset, d)
+    if isinstance(want, tuple):
+        want = want[0]
+    assert pc.compare_bf16(oracle, got_a, want)[0] == 0

@@ -22,6 +22,7 @@ FLAG_NO_PDL = 4096
 FLAG_SHORT_WAITS = 8192
 FLAG_NO_TAIL_HELP = 32768
 FLAG_NO_CLUSTER_SPLIT, FLAG_FORCE_CLUSTER_SPLIT = 65536, 131072
+FLAG_NO_TAIL_STAGING = 262144
 # timing diagnostics (D is garbage): honoured only with XEFUSE_ALLOW_DIAG=1 in the environment
 FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA, FLAG_DIAG_NO_EPILOGUE, FLAG_DIAG_NO_STORE = 256, 512, 1024, 2048
 STATIC_WORKSPACE_BYTES = 2097152

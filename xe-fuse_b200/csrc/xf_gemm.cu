@@ -638,6 +638,36 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
                    (uint64_t)d->ldd * 2, sd2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
       return XF_ERR_INTERNAL;
   }
+  // Epilogue operand of each CTA's last tile through TMA (see GemmParams::tm_opnd): the cos_sin
+  // table when the epilogue rotates pairs, else the residual; only where TMA can address it.
+  p.tail_opnd = 0;
+  if (v->kc == 1 && d->dtype_d != XF_DT_S32 && !(d->flags & XF_FLAG_NO_TAIL_STAGING)) {
+    const bool multi = d->L > 1;
+    if (e.pair == XF_PAIR_ROPE) {
+      const int P = e.cos_sin_period;
+      const xf_mat& m = e.cos_sin;
+      if (P > 0 && P <= 128 && v->bn % P == 0 && m.dtype == XF_DT_F32 && aligned16(m.ptr) &&
+          (m.ld * 4) % 16 == 0 && (!multi || (m.batch_stride > 0 && (m.batch_stride * 4) % 16 == 0))) {
+        const uint64_t s2 = multi ? (uint64_t)m.batch_stride * 4 : (uint64_t)m.ld * 4 * d->M;
+        if (encode_3d(&p.tm_opnd, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, m.ptr, P, d->M, d->L, (uint64_t)m.ld * 4, s2,
+                      32, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
+          p.tail_opnd = 2;
+          p.tail_opnd_boxes = P / 32;
+        }
+      }
+    } else if (e.residual.enabled) {
+      const xf_mat& m = e.residual;
+      if (m.dtype == XF_DT_BF16 && aligned16(m.ptr) && (m.ld * 2) % 16 == 0 &&
+          (!multi || (m.batch_stride > 0 && (m.batch_stride * 2) % 16 == 0))) {
+        const uint64_t s2 = multi ? (uint64_t)m.batch_stride * 2 : (uint64_t)m.ld * 2 * d->M;
+        if (encode_3d(&p.tm_opnd, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, m.ptr, d->N, d->M, d->L, (uint64_t)m.ld * 2,
+                      s2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
+          p.tail_opnd = 1;
+          p.tail_opnd_boxes = v->bn / 64;
+        }
+      }
+    }
+  }
   p.num_d_peer = d->num_d_peer;
   for (int c = 0; c < d->num_d_peer; ++c) {
     p.D_peer[c] = d->D_peer[c];

@@ -71,14 +71,12 @@ struct TileCfg {
   static constexpr int SMEM_BYTES =
       1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;             // double-buffered accumulator
-  // Cluster split-K: once the main loop is over, the pipeline stages receive the other K groups'
-  // partial accumulators of the columns this CTA finishes: (KC-1) x 128 rows x BN/KC columns x 4 B,
-  // behind the 16 KB the tail-helper warps stage their stores in.
+  // Cluster split-K: the pipeline stage the MMAs leave first receives the other K groups' partial
+  // accumulators of the columns this CTA finishes: (KC-1) x 128 rows x BN/KC columns x 4 B.
   static constexpr int XCHG_SLICES = BN / KC / 32;     // 32-column accumulator slices per K group
-  static constexpr int XCHG_OFF = 4 * EPI_BUFS * EPI_BUF_BYTES;
   static constexpr int XCHG_BYTES = (KC - 1) * BM * (BN / KC) * 4;
   static_assert(KC == 1 || (CTAS == 2 && BN == 256), "cluster split-K is built for paired 256-column tiles");
-  static_assert(KC == 1 || XCHG_OFF + XCHG_BYTES <= STAGES * STAGE_BYTES, "exchange buffer exceeds the stages");
+  static_assert(KC == 1 || (XCHG_BYTES <= STAGE_BYTES && STAGES >= 3), "exchange buffer exceeds a stage");
   static_assert(NGRP >= 1, "B tile narrower than one 128-byte column group");
   static_assert(TMEM_COLS == 256 || TMEM_COLS == 512 || TMEM_COLS == 128, "TMEM columns");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
@@ -285,6 +283,26 @@ __device__ __forceinline__ void load_mat_row32(const MatArg& m, int l, int row, 
   mat_row32_finish(mode, raw, m, l, row, col0, ncols_total, out);
 }
 
+// The same 32 elements out of an operand tile that TMA staged in shared memory: boxes of 128 rows x
+// 128 bytes (64 bf16 or 32 fp32 columns) with the 128-byte swizzle, one after the other.  `col` is
+// the column inside the staged tile (a multiple of 32), `r` the row inside the CTA tile.  Eight
+// consecutive lanes read eight different 16-byte positions, so the loads are conflict-free.
+__device__ __forceinline__ void mat_row32_from_smem(const uint8_t* tile, bool bf16, int r, int col,
+                                                    uint4 (&raw)[8]) {
+  if (bf16) {
+    const uint8_t* row = tile + (col >> 6) * 16384 + r * 128;
+    const int c0 = (col & 63) >> 3;          // first 16-byte chunk of the 32 columns inside the 128-byte row
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      raw[j] = *reinterpret_cast<const uint4*>(row + (((c0 + j) ^ (r & 7)) << 4));
+  } else {
+    const uint8_t* row = tile + (col >> 5) * 16384 + r * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      raw[j] = *reinterpret_cast<const uint4*>(row + ((j ^ (r & 7)) << 4));
+  }
+}
+
 // Column of the cos_sin operand that output column gcol reads, and the operand's width.
 __device__ __forceinline__ int cos_sin_col(const EpiParams& e, int gcol) {
   return e.cos_sin_period > 0 ? (gcol % e.cos_sin_period) : gcol;
@@ -473,6 +491,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* tail_bar = bars + 2 * STAGES + 6;    // [1]        the CTA's last accumulator is complete
   uint64_t* xfree_bar = bars + 2 * STAGES + 7;   // [1]  KC>1: the other K groups' stages are idle
   uint64_t* xdata_bar = bars + 2 * STAGES + 8;   // [1]  KC>1: their partial accumulators have landed
+  uint64_t* opnd_bar = bars + 2 * STAGES + 9;    // [1]  the last tile's staged epilogue operand has landed
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -488,9 +507,14 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   const int total_items = p.total_items;
   const long long budget = p.wait_budget;
 
+  // The full-matrix epilogue operand of the CTA's last tile is staged in shared memory when one
+  // tile of it fits a pipeline stage (and the variant keeps its idle stages free for it).
+  const bool tail_opnd = (KC == 1) && p.tail_opnd != 0 && p.tail_opnd_boxes * 16384 <= C::STAGE_BYTES &&
+                         STAGES >= 3;
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tmap(&p.tm_a);
     ptx::prefetch_tmap(&p.tm_b);
+    if (tail_opnd) ptx::prefetch_tmap(&p.tm_opnd);
     if (!p.direct_store && p.d_dtype == DT_BF16) ptx::prefetch_tmap(&p.tm_d);
   }
   if (warp == 1 && lane == 0) {
@@ -504,6 +528,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         ptx::mbar_init(ptx::smem_u32(tail_bar), 1);
         ptx::mbar_init(ptx::smem_u32(xfree_bar), KC > 1 ? KC - 1 : 1);
         ptx::mbar_init(ptx::smem_u32(xdata_bar), KC > 1 ? (KC - 1) * xchg_warps * 32 : 1);
+        ptx::mbar_init(ptx::smem_u32(opnd_bar), 1);
       }
       ptx::mbar_init(ptx::smem_u32(&tempty_bar[b]), C::EPI_WARPS * CTAS);
     }
@@ -592,7 +617,36 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if constexpr (KC > 1) break;   // one tile per cluster: the stages become the exchange buffer
+        if constexpr (KC > 1) {
+          // One tile per cluster.  The stage that would take the next K block is the first one the
+          // MMAs leave: it becomes the buffer the other K groups write their partials into, and they
+          // are told as soon as it is idle, a couple of K blocks before the accumulator is complete.
+          if (ok && ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, budget)) {
+#pragma unroll
+            for (int g = 0; g < KC; ++g)
+              if (g != static_cast<int>(kc))
+                ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(xfree_bar), g * CTAS + cta_rank));
+          } else if (ok && p.status) {
+            atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_PRODUCER_EMPTY);
+          }
+          break;
+        }
+        if (tail_opnd && ok && w + num_clusters >= total_items && wi.split_idx < 0) {
+          // Last tile of this CTA: the stage that would take the next K block is the first one the
+          // MMAs leave; it receives this CTA's 128 rows of the operand (own barrier, own memory).
+          if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, budget)) {
+            if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_PRODUCER_EMPTY);
+            break;
+          }
+          const uint32_t ob = ptx::smem_u32(opnd_bar);
+          ptx::mbar_arrive_expect_tx(ob, static_cast<uint32_t>(p.tail_opnd_boxes) * 16384u);
+          const uint32_t dst = ptx::smem_u32(stage_base + stage * C::STAGE_BYTES);
+          const int box_cols = p.tail_opnd == 1 ? 64 : 32;
+          const int c0 = p.tail_opnd == 1 ? tc.tn * BN : 0;   // the table is read from its first column
+          for (int b = 0; b < p.tail_opnd_boxes; ++b)
+            ptx::tma_load_3d<1>(dst + static_cast<uint32_t>(b) * 16384u, &p.tm_opnd, ob, c0 + b * box_cols,
+                                row0, tc.l);
+        }
       }
     }
   } else if (warp == 1) {
@@ -671,6 +725,8 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     uint8_t* stg = helper ? stage_base + warp * (C::EPI_BUFS * C::EPI_BUF_BYTES)
                           : epi_base + ew * (C::EPI_BUFS * C::EPI_BUF_BYTES);
     int sidx = 0;
+    int kb_seen = 0;                        // K blocks this CTA's pipeline has carried so far
+    const uint8_t* staged = nullptr;        // the last tile's operand tile in shared memory, if staged
     const bool compact = e.compact != 0;
     const int n_out = compact ? (p.N >> 1) : p.N;
     const int slices_per_unit = compact ? 2 : 1;   // 32 output columns = 1 or 2 accumulator slices
@@ -683,6 +739,21 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       const WorkItem wi = decode_item(p, schedule_item(p, w, cluster_idx, num_clusters));
       // the CTA's last item, if it is a whole tile, is shared three ways per quadrant
       const bool shared3 = (w + num_clusters >= total_items || KC > 1) && wi.split_idx < 0 && !(p.diag & 16);
+      kb_seen += wi.kb1 - wi.kb0;
+      const bool use_staged = tail_opnd && (w + num_clusters >= total_items) && wi.split_idx < 0;
+      if (KC > 1 && helper) {   // off the stage that receives the other groups' partials
+        const int nkb_item = wi.kb1 - wi.kb0;
+        const int mine = (nkb_item * (static_cast<int>(kc) + 1) / KC - nkb_item * static_cast<int>(kc) / KC) % STAGES;
+        stg = stage_base + ((mine + 1) % STAGES) * C::STAGE_BYTES + warp * (C::EPI_BUFS * C::EPI_BUF_BYTES);
+      }
+      if (use_staged) {
+        // the producer put the operand in the stage after the last K block's; the helpers' store
+        // staging moves to the stage after that one
+        const int sx = kb_seen % STAGES;
+        staged = stage_base + sx * C::STAGE_BYTES;
+        if (helper)
+          stg = stage_base + ((sx + 1) % STAGES) * C::STAGE_BYTES + warp * (C::EPI_BUFS * C::EPI_BUF_BYTES);
+      }
       const TileCoord tc = decode_tile(p, wi.tile);
       const int buf = it & 1;
       const int m0 = (tc.tm * CTAS + static_cast<int>(cta_rank)) * C::BM;
@@ -711,6 +782,10 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         break;
       }
       ptx::tc_fence_after();
+      if (use_staged && !ptx::mbar_wait(ptx::smem_u32(opnd_bar), 0u, budget)) {
+        if (p.status && lane == 0) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_EPI_OPERAND);
+        break;
+      }
 
       const uint32_t t_row = tmem_base + static_cast<uint32_t>(buf * BN) +
                              (static_cast<uint32_t>(q * 32) << 16);
@@ -793,15 +868,12 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       if constexpr (KC > 1) {
         constexpr int SPG = C::XCHG_SLICES;
         const uint32_t xfree = ptx::smem_u32(xfree_bar), xdata = ptx::smem_u32(xdata_bar);
-        const uint32_t xbuf = ptx::smem_u32(stage_base + C::XCHG_OFF);
         const int workers = shared3 ? 3 : 2;
+        const int nkb_item = wi.kb1 - wi.kb0;
+        // receive stage of K group g: the ring slot after its last K block (its producer said so)
+        auto recv_stage = [&](int g) { return (nkb_item * (g + 1) / KC - nkb_item * g / KC) % STAGES; };
         bool ok = true;
-        // this CTA's MMAs are done (the accumulator barrier has completed): its stages are idle
-        if (warp == 4 && lane == 0) {
-#pragma unroll
-          for (int g = 0; g < KC; ++g)
-            if (g != static_cast<int>(kc)) ptx::mbar_arrive_cluster(ptx::mapa(xfree, g * CTAS + cta_rank));
-        }
+        // every other group's receive stage is idle (signalled by its producer warp)
         if (!ptx::mbar_wait_cluster(xfree, 0u, budget)) ok = false;
         if (ok) {
           for (int idx = half; idx < (KC - 1) * SPG; idx += workers) {
@@ -812,6 +884,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(g * (BN / KC) + sl * 32), r);
             ptx::tmem_ld_wait();
             // receiver layout [sender slot][slice][16-byte chunk][row]: a warp's store is 512 contiguous bytes
+            const uint32_t xbuf = ptx::smem_u32(stage_base + recv_stage(g) * C::STAGE_BYTES);
             const uint32_t dst = ptx::mapa(xbuf, g * CTAS + cta_rank) +
                                  static_cast<uint32_t>((((slot * SPG + sl) * 8) * C::BM + q * 32 + lane) * 16);
 #pragma unroll
@@ -832,7 +905,8 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         const int upg = SPG / slices_per_unit;                  // output units per K group
         u_first = static_cast<int>(kc) * upg + half;
         u_end = min(nunits, (static_cast<int>(kc) + 1) * upg);
-        xrecv = reinterpret_cast<const uint4*>(stage_base + C::XCHG_OFF) + (q * 32 + lane);
+        xrecv = reinterpret_cast<const uint4*>(stage_base + recv_stage(static_cast<int>(kc)) * C::STAGE_BYTES) +
+                (q * 32 + lane);
       }
 
       for (int u = u_first; u < u_end; u += u_step) {
@@ -851,10 +925,15 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           uint4 pre[8];
           int pre_mode = 0;
           if (row_ok && !(p.diag & 4) && p.d_dtype != DT_S32) {
-            if (pre_which == PRE_RESIDUAL)
+            if (use_staged) {        // staged by TMA while the main loop drained: no global access
+              mat_row32_from_smem(staged, pre_which == PRE_RESIDUAL, q * 32 + lane,
+                                  pre_which == PRE_RESIDUAL ? tcol0 : cos_sin_col(e, n0 + tcol0), pre);
+              pre_mode = 1;
+            } else if (pre_which == PRE_RESIDUAL) {
               pre_mode = mat_row32_issue(e.residual, l, row, n0 + tcol0, p.N, pre);
-            else if (pre_which == PRE_COS_SIN)
+            } else if (pre_which == PRE_COS_SIN) {
               pre_mode = mat_row32_issue(e.cos_sin, l, row, cos_sin_col(e, n0 + tcol0), cos_sin_width(e, p.N), pre);
+            }
           }
           if (part_base == nullptr) {
             ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);

@@ -19,6 +19,7 @@ enum : int {
   DEV_TIMEOUT_EPI_TMEM_FULL = 4,
   DEV_TIMEOUT_SPLIT_PARTIALS = 5,   // a K slice never saw the other slices' partial accumulators
   DEV_TIMEOUT_CLUSTER_EXCHANGE = 6, // cluster split-K: the other K groups' partials never arrived
+  DEV_TIMEOUT_EPI_OPERAND = 7,      // the staged epilogue operand of the last tile never landed
 };
 
 struct VecArg {
@@ -57,6 +58,10 @@ struct alignas(64) GemmParams {
   CUtensorMap tm_b;   // [L][K][N], box {128 B of N, KBLK rows}, 128-B swizzle
   CUtensorMap tm_d;   // [L][M][Nout] bf16, box {32 cols, 32 rows}, 64-B swizzle
   CUtensorMap tm_d_peer[7];  // further copies of D (other GPUs' gathered buffers), same geometry
+  // Full-matrix epilogue operand of a CTA's LAST tile, fetched by TMA into an idle pipeline stage
+  // while that tile's main loop drains (tail_opnd != 0): residual bf16 [L][M][N], box {64 cols,
+  // 128 rows}; or the per-head cos_sin table fp32 [L][M][P], box {32 cols, 128 rows}; 128-B swizzle.
+  CUtensorMap tm_opnd;
   int M, N, K, L;
   int tiles_m, tiles_n;    // in units of the cluster tile (128*CTAS rows x BN columns)
   int num_kb;              // ceil(K / KBLK)
@@ -70,6 +75,8 @@ struct alignas(64) GemmParams {
   long long ldd, batch_d;
   int d_dtype;             // DT_BF16 / DT_F32 / DT_S32
   int direct_store;        // 1: plain global stores for D
+  int tail_opnd;           // 0 none, 1 residual, 2 cos_sin table: what tm_opnd describes
+  int tail_opnd_boxes;     // boxes of 16 KB that make up one CTA tile of that operand
   int diag;                // diagnostics: bit0 skip the TMA loads, bit1 skip the MMAs (results are garbage)
   int* status;             // device status word (may be null)
   // Split-K of the remainder wave: work items [0, split_first) are whole tiles; the tiles from
