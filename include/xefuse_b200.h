@@ -198,6 +198,9 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_NO_TAIL_STAGING 262144 /* a CTA's last tile reads its residual / cos_sin operand with plain
                                     loads like every other tile (by default TMA stages that one tile's
                                     operand in an idle pipeline stage while the main loop drains) */
+#define XF_FLAG_NO_ACC_PREFETCH 524288 /* the epilogue reads each 32-column accumulator slice out of tensor
+                                    memory when it needs it (by default a warp requests its next slice
+                                    while it works on the current one, where it has registers to spare) */
 #define XF_FLAG_FORCE_CLUSTER_SPLIT 131072 /* use a cluster split-K variant whenever K is long enough, also
                                     for problems with more tiles than co-resident clusters */
 
@@ -208,7 +211,8 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_DIAG_NO_MMA   512    /* skip the tensor-core MMAs */
 #define XF_FLAG_DIAG_NO_EPILOGUE 1024 /* drain TMEM, compute and store nothing */
 #define XF_FLAG_DIAG_NO_STORE 2048   /* run the epilogue math, store nothing */
-#define XF_FLAG_DIAG_MASK (256 | 512 | 1024 | 2048)
+#define XF_FLAG_DIAG_NO_ACC_READ 1048576 /* the epilogue works on zeros instead of reading tensor memory */
+#define XF_FLAG_DIAG_MASK (256 | 512 | 1024 | 2048 | 1048576)
 
 typedef struct xf_plan xf_plan;
 

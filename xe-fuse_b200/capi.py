@@ -23,8 +23,10 @@ FLAG_SHORT_WAITS = 8192
 FLAG_NO_TAIL_HELP = 32768
 FLAG_NO_CLUSTER_SPLIT, FLAG_FORCE_CLUSTER_SPLIT = 65536, 131072
 FLAG_NO_TAIL_STAGING = 262144
+FLAG_NO_ACC_PREFETCH = 524288
 # timing diagnostics (D is garbage): honoured only with XEFUSE_ALLOW_DIAG=1 in the environment
 FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA, FLAG_DIAG_NO_EPILOGUE, FLAG_DIAG_NO_STORE = 256, 512, 1024, 2048
+FLAG_DIAG_NO_ACC_READ = 1048576
 STATIC_WORKSPACE_BYTES = 2097152
 
 STATUS_NAMES = ["XF_SUCCESS", "XF_ERR_MISALIGNED_OPERAND", "XF_ERR_INVALID_DATA_TYPE",

@@ -190,6 +190,52 @@ __device__ __forceinline__ void load_vec32(const VecArg& a, int l, int col0, int
   }
 }
 
+// v[i] = v[i] * a[col0 + i] (MUL) or v[i] + a[col0 + i] over 32 consecutive elements of a per-column
+// vector, consumed 16 bytes at a time so no 32-element temporary is alive beside v.  Every lane of a
+// warp reads the same addresses (one L1 transaction per load); columns >= n_total count as `fill`.
+template <bool MUL>
+__device__ __forceinline__ void apply_vec32(const VecArg& a, int l, int col0, int n_total, float fill,
+                                            float (&v)[32]) {
+  auto op = [](float x, float y) { return MUL ? x * y : x + y; };
+  if (a.ptr == nullptr) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = op(v[i], a.null_default);
+    return;
+  }
+  const long long off = static_cast<long long>(l) * a.batch_stride + col0;
+  if (a.dtype == DT_BF16) {
+    const __nv_bfloat16* ptr = reinterpret_cast<const __nv_bfloat16*>(a.ptr) + off;
+    if (col0 + 32 <= n_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(ptr) + j);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          v[j * 8 + t * 2 + 0] = op(v[j * 8 + t * 2 + 0], __uint_as_float(w[t] << 16));
+          v[j * 8 + t * 2 + 1] = op(v[j * 8 + t * 2 + 1], __uint_as_float(w[t] & 0xFFFF0000u));
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = op(v[i], (col0 + i < n_total) ? __bfloat162float(ptr[i]) : fill);
+    }
+  } else {
+    const float* ptr = reinterpret_cast<const float*>(a.ptr) + off;
+    if (col0 + 32 <= n_total && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(ptr) + j);
+        v[j * 4 + 0] = op(v[j * 4 + 0], f.x); v[j * 4 + 1] = op(v[j * 4 + 1], f.y);
+        v[j * 4 + 2] = op(v[j * 4 + 2], f.z); v[j * 4 + 3] = op(v[j * 4 + 3], f.w);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = op(v[i], (col0 + i < n_total) ? ptr[i] : fill);
+    }
+  }
+}
+
 __device__ __forceinline__ float unary_apply(int op, float x) {
   switch (op) {
     case UN_GELU: return x * 0.5f * (1.0f + erff(x * 0.7071067811865475f));
@@ -365,21 +411,55 @@ __device__ __forceinline__ void store_bf16_row(__nv_bfloat16* ptr, const uint32_
 //   gcol0  global column of r[0]
 //   pre_which / pre_mode / pre   the full-matrix operand whose loads were issued ahead of the
 //          accumulator read (mat_row32_issue), if any; the other one is loaded here
+//   staged / srow / scol   the operand tile TMA staged in shared memory for a CTA's last tile (or
+//          null), this thread's row in it and the first of the 32 columns; it takes the place of
+//          `pre`, whose registers then carry the next accumulator slice
+__device__ __forceinline__ void rope_pair(float xe, float xo, float c, float s, float& oe, float& oo) {
+  oe = xe * c + xo * s;
+  oo = -xe * s + xo * c;
+}
+
 template <int KIND>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const uint32_t (&r)[32],
                                                float (&v)[32], int row, bool row_ok, int l,
                                                int gcol0, float rs, int pre_which, int pre_mode,
-                                               const uint4 (&pre)[8]) {
+                                               const uint4 (&pre)[8], const uint8_t* staged, int srow,
+                                               int scol) {
 #pragma unroll
   for (int i = 0; i < 32; ++i)
     v[i] = (KIND == 0) ? __uint_as_float(r[i]) : static_cast<float>(static_cast<int>(r[i]));
 
   if (e.residual.enabled && row_ok) {
-    float t[32];
-    if (pre_which == PRE_RESIDUAL) mat_row32_finish(pre_mode, pre, e.residual, l, row, gcol0, N, t);
-    else load_mat_row32(e.residual, l, row, gcol0, N, t);
+    if (staged != nullptr && pre_which == PRE_RESIDUAL) {
+      const uint8_t* srow_ptr = staged + (scol >> 6) * 16384 + srow * 128;
+      const int c0 = (scol & 63) >> 3;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] += t[i];
+      for (int j = 0; j < 4; ++j) {
+        const uint4 x = *reinterpret_cast<const uint4*>(srow_ptr + (((c0 + j) ^ (srow & 7)) << 4));
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          v[j * 8 + t * 2 + 0] += __uint_as_float(w[t] << 16);
+          v[j * 8 + t * 2 + 1] += __uint_as_float(w[t] & 0xFFFF0000u);
+        }
+      }
+    } else if (pre_which == PRE_RESIDUAL && pre_mode == 1 && e.residual.dtype == DT_BF16) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {     // the words requested ahead of the accumulator read
+        const uint32_t w[4] = {pre[j].x, pre[j].y, pre[j].z, pre[j].w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          v[j * 8 + t * 2 + 0] += __uint_as_float(w[t] << 16);
+          v[j * 8 + t * 2 + 1] += __uint_as_float(w[t] & 0xFFFF0000u);
+        }
+      }
+    } else {
+      float t[32];
+      if (pre_which == PRE_RESIDUAL) mat_row32_finish(pre_mode, pre, e.residual, l, row, gcol0, N, t);
+      else load_mat_row32(e.residual, l, row, gcol0, N, t);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] += t[i];
+    }
   }
   if (e.aux_store.enabled && row_ok) {
     uint32_t pk[16];
@@ -394,18 +474,8 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] *= rs;
   }
-  if (e.col_scale.enabled) {
-    float t[32];
-    load_vec32(e.col_scale, l, gcol0, N, 1.0f, t);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= t[i];
-  }
-  if (e.bias.enabled) {
-    float t[32];
-    load_vec32(e.bias, l, gcol0, N, 0.0f, t);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] += t[i];
-  }
+  if (e.col_scale.enabled) apply_vec32<true>(e.col_scale, l, gcol0, N, 1.0f, v);
+  if (e.bias.enabled) apply_vec32<false>(e.bias, l, gcol0, N, 0.0f, v);
   // The op switches sit OUTSIDE the element loops: every loop body is straight-line code, so the
   // 32 independent elements of a chunk interleave instead of running as one dependent chain each.
   switch (e.unary) {
@@ -442,22 +512,36 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
       for (int j = 0; j < 16; ++j) { v[2 * j] = o[j]; v[2 * j + 1] = o[j]; }
     }
   } else if (e.pair == PAIR_ROPE) {
-    float cs[32];
-    if (row_ok) {
-      const int ccol = cos_sin_col(e, gcol0);
-      const int climit = cos_sin_width(e, N);
-      if (pre_which == PRE_COS_SIN) mat_row32_finish(pre_mode, pre, e.cos_sin, l, row, ccol, climit, cs);
-      else load_mat_row32(e.cos_sin, l, row, ccol, climit, cs);
+    if (staged != nullptr && pre_which == PRE_COS_SIN && row_ok) {
+      const uint8_t* srow_ptr = staged + (scol >> 5) * 16384 + srow * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 x = *reinterpret_cast<const uint4*>(srow_ptr + ((j ^ (srow & 7)) << 4));
+        rope_pair(v[4 * j], v[4 * j + 1], __uint_as_float(x.x), __uint_as_float(x.y), v[4 * j], v[4 * j + 1]);
+        rope_pair(v[4 * j + 2], v[4 * j + 3], __uint_as_float(x.z), __uint_as_float(x.w), v[4 * j + 2],
+                  v[4 * j + 3]);
+      }
+    } else if (pre_which == PRE_COS_SIN && pre_mode == 1 && row_ok) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {     // the words requested ahead of the accumulator read
+        rope_pair(v[4 * j], v[4 * j + 1], __uint_as_float(pre[j].x), __uint_as_float(pre[j].y), v[4 * j],
+                  v[4 * j + 1]);
+        rope_pair(v[4 * j + 2], v[4 * j + 3], __uint_as_float(pre[j].z), __uint_as_float(pre[j].w),
+                  v[4 * j + 2], v[4 * j + 3]);
+      }
     } else {
+      float cs[32];
+      if (row_ok) {
+        const int ccol = cos_sin_col(e, gcol0);
+        const int climit = cos_sin_width(e, N);
+        if (pre_which == PRE_COS_SIN) mat_row32_finish(pre_mode, pre, e.cos_sin, l, row, ccol, climit, cs);
+        else load_mat_row32(e.cos_sin, l, row, ccol, climit, cs);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) cs[i] = 0.0f;
-    }
+        for (int i = 0; i < 32; ++i) cs[i] = 0.0f;
+      }
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float xe = v[2 * j], xo = v[2 * j + 1];
-      const float c = cs[2 * j], s = cs[2 * j + 1];
-      v[2 * j] = xe * c + xo * s;
-      v[2 * j + 1] = -xe * s + xo * c;
+      for (int j = 0; j < 16; ++j) rope_pair(v[2 * j], v[2 * j + 1], cs[2 * j], cs[2 * j + 1], v[2 * j], v[2 * j + 1]);
     }
   } else if (e.pair == PAIR_SWAP) {
 #pragma unroll
@@ -576,6 +660,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         // cluster split-K: this pair takes the kc-th of KC equal parts of the item's K range
         const int kb_lo = (KC > 1) ? wi.kb0 + static_cast<int>(kc) * (wi.kb1 - wi.kb0) / KC : wi.kb0;
         const int kb_hi = (KC > 1) ? wi.kb0 + static_cast<int>(kc + 1) * (wi.kb1 - wi.kb0) / KC : wi.kb1;
+        // (Every tile walks K from its first block.  Starting tiles that share an operand panel at
+        // different K blocks was tried and is slower: CTAs that ask L2 for the same lines at the
+        // same time are served together.)
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, budget)) {
             if (p.status) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_PRODUCER_EMPTY);
@@ -909,6 +996,14 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
                 (q * 32 + lane);
       }
 
+      // One 32-register group per thread serves two purposes.  Where the epilogue reads a residual /
+      // cos_sin operand from global memory it holds that operand's words, requested before the
+      // accumulator slice is read.  Otherwise (no such operand, or the operand staged in shared
+      // memory) it receives the NEXT accumulator slice of this warp while the current one is being
+      // processed, so the TMEM read latency is paid once per tile instead of once per slice.
+      uint4 pre[8];
+      const bool acc_prefetch = part_base == nullptr && (pre_which == PRE_NONE || use_staged) && !(p.diag & 32);
+      bool prefetched = false;
       for (int u = u_first; u < u_end; u += u_step) {
         uint32_t pk[16];
         const bool last_unit = (u + u_step >= u_end);
@@ -922,23 +1017,37 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           uint32_t r[32];
           const int tcol0 = s * 32;
           // the residual / cos_sin loads of this slice go out before the accumulator is read
-          uint4 pre[8];
           int pre_mode = 0;
-          if (row_ok && !(p.diag & 4) && p.d_dtype != DT_S32) {
-            if (use_staged) {        // staged by TMA while the main loop drained: no global access
-              mat_row32_from_smem(staged, pre_which == PRE_RESIDUAL, q * 32 + lane,
-                                  pre_which == PRE_RESIDUAL ? tcol0 : cos_sin_col(e, n0 + tcol0), pre);
-              pre_mode = 1;
-            } else if (pre_which == PRE_RESIDUAL) {
+          if (!acc_prefetch && !use_staged && row_ok && !(p.diag & 4) && p.d_dtype != DT_S32) {
+            if (pre_which == PRE_RESIDUAL)
               pre_mode = mat_row32_issue(e.residual, l, row, n0 + tcol0, p.N, pre);
-            } else if (pre_which == PRE_COS_SIN) {
+            else if (pre_which == PRE_COS_SIN)
               pre_mode = mat_row32_issue(e.cos_sin, l, row, cos_sin_col(e, n0 + tcol0), cos_sin_width(e, p.N), pre);
-            }
           }
           if (part_base == nullptr) {
-            ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
-            ptx::tmem_ld_wait();
-            if (last_unit && (h + 1 == slices_per_unit || s + 1 >= nsub)) release_tmem();
+            // this warp's next slice of the tile, if any
+            const bool more_in_unit = (h + 1 < slices_per_unit) && (s + 1 < nsub);
+            const bool has_next = more_in_unit || (u + u_step < u_end);
+            const int next_s = more_in_unit ? s + 1 : (u + u_step) * slices_per_unit;
+            if (prefetched) {
+              ptx::tmem_ld_wait_for(pre);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                r[4 * j] = pre[j].x; r[4 * j + 1] = pre[j].y; r[4 * j + 2] = pre[j].z; r[4 * j + 3] = pre[j].w;
+              }
+              prefetched = false;
+            } else if (p.diag & 64) {   // diagnostics: no accumulator read
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            } else {
+              ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(tcol0), r);
+              ptx::tmem_ld_wait();
+            }
+            if (acc_prefetch && has_next && !(p.diag & 64)) {
+              ptx::tmem_ld_32x32_async(t_row + static_cast<uint32_t>(next_s * 32), pre);
+              prefetched = true;
+            }
+            if (!has_next) release_tmem();
             if constexpr (KC > 1) {
               // add the other K groups' partials of this slice, in group order
               const int sl = s - static_cast<int>(kc) * C::XCHG_SLICES;
@@ -1016,7 +1125,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             stored_direct = true;
             continue;
           }
-          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs, pre_which, pre_mode, pre);
+          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs, pre_which, pre_mode, pre,
+                               use_staged ? staged : nullptr, q * 32 + lane,
+                               pre_which == PRE_RESIDUAL ? tcol0 : cos_sin_col(e, n0 + tcol0));
           if (e.row_sumsq != nullptr) {
             // side output for a following RMSNorm: this row's sum of squares over these 32 columns
             const int nv = p.N - (n0 + tcol0);

@@ -292,6 +292,34 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same load into eight 16-byte register groups, for a load that is left in flight while other
+// work runs, and the wait that ends it.  The wait names the destination registers as read-write
+// operands, so the compiler orders every later use of them after it.
+__device__ __forceinline__ void tmem_ld_32x32_async(uint32_t taddr, uint4 (&a)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(a[0].x), "=r"(a[0].y), "=r"(a[0].z), "=r"(a[0].w), "=r"(a[1].x), "=r"(a[1].y), "=r"(a[1].z),
+        "=r"(a[1].w), "=r"(a[2].x), "=r"(a[2].y), "=r"(a[2].z), "=r"(a[2].w), "=r"(a[3].x), "=r"(a[3].y),
+        "=r"(a[3].z), "=r"(a[3].w), "=r"(a[4].x), "=r"(a[4].y), "=r"(a[4].z), "=r"(a[4].w), "=r"(a[5].x),
+        "=r"(a[5].y), "=r"(a[5].z), "=r"(a[5].w), "=r"(a[6].x), "=r"(a[6].y), "=r"(a[6].z), "=r"(a[6].w),
+        "=r"(a[7].x), "=r"(a[7].y), "=r"(a[7].z), "=r"(a[7].w)
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_for(uint4 (&a)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(a[0].x), "+r"(a[0].y), "+r"(a[0].z), "+r"(a[0].w), "+r"(a[1].x), "+r"(a[1].y),
+                 "+r"(a[1].z), "+r"(a[1].w), "+r"(a[2].x), "+r"(a[2].y), "+r"(a[2].z), "+r"(a[2].w),
+                 "+r"(a[3].x), "+r"(a[3].y), "+r"(a[3].z), "+r"(a[3].w), "+r"(a[4].x), "+r"(a[4].y),
+                 "+r"(a[4].z), "+r"(a[4].w), "+r"(a[5].x), "+r"(a[5].y), "+r"(a[5].z), "+r"(a[5].w),
+                 "+r"(a[6].x), "+r"(a[6].y), "+r"(a[6].z), "+r"(a[6].w), "+r"(a[7].x), "+r"(a[7].y),
+                 "+r"(a[7].z), "+r"(a[7].w)
+               :
+               : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05.mma
 // D[tmem] (+)= A[smem desc] * B[smem desc].  KIND: 0 = kind::f16 (bf16/fp16 in, fp32 acc),
 // 1 = kind::i8 (int8 in, int32 acc).  Issued by ONE thread.
