@@ -419,13 +419,40 @@ class Workload:
                 if s["plan"].device_status() != 0:
                     raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
 
+    def graph_of(self, n):
+        """A CUDA graph of `n` consecutive steps (single GPU, kernels only): a step of a small
+        workload lasts 20-40 us, about what a launch through Python costs, so its steps are
+        replayed from a graph instead of being launched one by one."""
+        torch = self.torch
+        s = torch.cuda.Stream(self.ctx["dev"])
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            self.step()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(n):
+                    self.step()
+        torch.cuda.synchronize()
+        return g
+
+    def small(self):
+        return self.world == 1 and len(self.rot) > 1 and not any(s["chain"] for s in self.gpu)
+
     def timed(self, steps, warmup):
         """(TFLOP/s whole job, ms per step): EXACTLY `steps` steps between two barriers."""
         barrier = self.ctx["barrier"]
         for _ in range(warmup):
             self.step()
         barrier()
-        ms = time_loop(self.torch, self.step, steps)
+        if self.small():
+            g = self.graph_of(steps)
+            g.replay()                       # one untimed replay: graph upload
+            barrier()
+            ms = time_loop(self.torch, g.replay, 1)
+            self.launch_mode = "CUDA graph of the timed steps"
+        else:
+            ms = time_loop(self.torch, self.step, steps)
+            self.launch_mode = "one launch call per kernel"
         barrier()
         ms = self.max_over_ranks(ms)
         self.check_status()
@@ -436,9 +463,20 @@ class Workload:
         barrier = self.ctx["barrier"]
         n = max(min_steps, min(20000, int(seconds / max(ms_per_step * 1e-3, 1e-6))))
         barrier()
-        t0 = time.time()
-        ms = time_loop(self.torch, self.step, n)
-        t1 = time.time()
+        if self.small():
+            per = 200
+            g = self.graph_of(per)
+            reps = max(1, n // per)
+            n = reps * per
+            g.replay()
+            barrier()
+            t0 = time.time()
+            ms = time_loop(self.torch, g.replay, reps)
+            t1 = time.time()
+        else:
+            t0 = time.time()
+            ms = time_loop(self.torch, self.step, n)
+            t1 = time.time()
         barrier()
         ms = self.max_over_ranks(ms)
         return self.flops_total * n / (ms * 1e-3) / 1e12, ms / n, (t0 + 0.1, t1), n
@@ -595,7 +633,22 @@ class Workload:
         for _ in range(3):
             ustep()
         ctx["barrier"]()
-        ms = time_loop(self.torch, ustep, steps)
+        if self.small():                     # replayed from a graph like the fused steps
+            torch = self.torch
+            st = torch.cuda.Stream(dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(st):
+                ustep()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g, stream=st):
+                    for _ in range(steps):
+                        ustep()
+            torch.cuda.synchronize()
+            g.replay()
+            ctx["barrier"]()
+            ms = time_loop(torch, g.replay, 1)
+        else:
+            ms = time_loop(self.torch, ustep, steps)
         ctx["barrier"]()
         ms = self.max_over_ranks(ms)
         v = self.flops_total * steps / (ms * 1e-3) / 1e12
@@ -606,7 +659,8 @@ class Workload:
         l2 = self.ctx["l2_bytes"]
         if len(self.rot) > 1:
             return (f"steps rotate over {len(self.rot)} independent copies of the working set "
-                    f"({(self.resident * len(self.rot)) >> 20} MiB in all > 2.5 x L2 {l2 >> 20} MiB), no flush")
+                    f"({(self.resident * len(self.rot)) >> 20} MiB in all > 2.5 x L2 {l2 >> 20} MiB), no flush; "
+                    f"{getattr(self, 'launch_mode', '')}")
         return f"resident inputs+outputs {self.resident >> 20} MiB > L2 {l2 >> 20} MiB, no flush"
 
 
