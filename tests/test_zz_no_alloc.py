@@ -78,7 +78,7 @@ def test_static_workspace_entry_runs_a_split_schedule_that_fits(capi, oracle, cu
     lib = capi.lib()
     lib.xf_gemm_run_static_workspace(None, None)          # first touch outside the memory accounting
     for seed in (23, 24):
-        _both_entries(capi, oracle, cuda, "k1", 256, 256, 4096, seed=seed,
+        _both_entries(capi, oracle, cuda, "k1", 128, 256, 4096, seed=seed,
                       flags=capi.FLAG_NO_CLUSTER_SPLIT, expect_in_name="ksplit")
 
 

@@ -49,7 +49,7 @@ def split_factor(tiles, units, K, es, bn, ks, eff, compact=False):
     if rem == 0:
         return 0
     num_kb = ceil(K / ((128 // es) * ks))
-    s = min(units // rem, num_kb // MIN_KB_PER_SLICE, MAX_SPLIT, bn // (64 if compact else 32))
+    s = min(units // rem, num_kb // MIN_KB_PER_SLICE, MAX_SPLIT)
     if s < 2:
         return 0
     return s if tile_time_us(bn, eff, K, es) * (1.0 - 1.0 / s) > split_overhead_us(bn, tiles >= units) else 0

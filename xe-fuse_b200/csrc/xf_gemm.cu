@@ -360,9 +360,9 @@ static int split_factor(const Variant& v, const xf_gemm_desc* d, int tiles, int 
   int s = units / rem;
   if (s > num_kb / kMinKbPerSlice) s = num_kb / kMinKbPerSlice;
   if (s > kMaxSplit) s = kMaxSplit;
-  // every slice finishes whole 32-output-column units of the tile
-  const int units_per_tile = v.bn / (d->epi.out_layout == XF_OUT_COMPACT ? 64 : 32);
-  if (s > units_per_tile) s = units_per_tile;
+  // Each slice finishes whole 32-output-column units of the tile (unit u goes to slice u mod S); with
+  // more slices than units (a compact 256-column tile has 4) the extra slices only contribute their
+  // partial sums.
   if (s < 2) return 0;
   const double t = tile_time_us(v, d->K, es);
   return t * (1.0 - 1.0 / s) > split_overhead_us(v, tiles >= units) ? s : 0;
