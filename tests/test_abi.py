@@ -145,3 +145,24 @@ def test_plan_create_without_gpu_fails_loudly(capi):
     h = C.c_void_p()
     rc = capi.lib().xf_gemm_plan_create(C.byref(d), None, C.byref(h))
     assert rc != 0 and not h.value
+
+
+def test_diagnostic_flags_need_an_opt_in(capi, monkeypatch):
+    """The XF_FLAG_DIAG_* flags leave D garbage: refused unless the environment opts in."""
+    d = base_desc(capi)
+    d.flags = capi.FLAG_DIAG_NO_MMA
+    monkeypatch.delenv("XEFUSE_ALLOW_DIAG", raising=False)
+    assert status(capi, d) == 5
+    assert b"XEFUSE_ALLOW_DIAG" in capi.lib().xf_last_error_string()
+    monkeypatch.setenv("XEFUSE_ALLOW_DIAG", "1")
+    assert status(capi, d) == 0
+    d.flags = capi.FLAG_NO_CLUSTER_SPLIT | capi.FLAG_NO_TAIL_STAGING | capi.FLAG_NO_ACC_PREFETCH   # plain tuning flags
+    monkeypatch.delenv("XEFUSE_ALLOW_DIAG", raising=False)
+    assert status(capi, d) == 0
+
+
+def test_static_workspace_entries_reject_null_arguments(capi):
+    L = capi.lib()
+    assert L.xf_gemm_run_static_workspace(None, None) == 4
+    assert L.xf_gemm_static_workspace_status(None) == 4
+    assert L.xf_gemm_cluster_capacity(capi.DT_F32, None, None) == 4
