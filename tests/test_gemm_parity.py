@@ -278,3 +278,40 @@ def test_tail_operand_staging_is_bit_identical(preset, shape, capi, oracle, cuda
     if isinstance(want, tuple):
         want = want[0]
     assert pc.compare_bf16(oracle, got_a, want)[0] == 0
+
+
+def test_batched_full_matrix_operands(capi, oracle, cuda):
+    """L > 1 with a residual (batch stride M*N) and with a per-head RoPE table (batch stride M*P):
+    the staged operand of the last tile takes its batch from the tile's batch index."""
+    import torch
+    from conftest import bf16_bits
+    L, M, N, K, P = 3, 200, 384, 160, 128
+    rng = np.random.default_rng(17)
+    A = oracle.f32_to_bf16(rng.standard_normal((L, M, K)).astype(np.float32))
+    B = oracle.f32_to_bf16((rng.standard_normal((L, K, N)) * K ** -0.5).astype(np.float32))
+    res = oracle.f32_to_bf16(rng.standard_normal((L, M, N)).astype(np.float32))
+    gamma = rng.normal(1.0, 0.02, (L, N)).astype(np.float32)
+    cs = np.stack([oracle.rope_table(M, P, 500000.0 * (l + 1)) for l in range(L)])
+    R = rng.uniform(0.5, 1.5, (L, M)).astype(np.float32)
+    tA, tB = _t(torch, A, cuda, True), _t(torch, B, cuda, True)
+    outs = {}
+    for flags in (0, capi.FLAG_NO_TAIL_STAGING):
+        D1 = torch.zeros((L, M, N), dtype=torch.bfloat16, device=cuda)
+        p1 = capi.GemmPlan(tA, tB, D1, residual=_t(torch, res, cuda, True), col_scale=_t(torch, gamma.reshape(-1), cuda),
+                           flags=flags)
+        p1.run()
+        D2 = torch.zeros((L, M, N), dtype=torch.bfloat16, device=cuda)
+        p2 = capi.GemmPlan(tA, tB, D2, row_scale=_t(torch, R.reshape(-1), cuda), pair="rope",
+                           cos_sin=_t(torch, cs, cuda), cos_sin_period=P, flags=flags)
+        p2.run()
+        torch.cuda.synchronize()
+        assert p1.device_status() == 0 and p2.device_status() == 0
+        outs[flags] = (bf16_bits(D1).copy(), bf16_bits(D2).copy())
+    assert np.array_equal(outs[0][0], outs[capi.FLAG_NO_TAIL_STAGING][0])
+    assert np.array_equal(outs[0][1], outs[capi.FLAG_NO_TAIL_STAGING][1])
+    for l in range(L):
+        acc = oracle.gemm_bf16(A[l], B[l])
+        want1 = oracle.epilogue(acc, residual=res[l], col=gamma[l])
+        assert pc.compare_bf16(oracle, outs[0][0][l], want1)[0] == 0
+        want2 = oracle.epilogue(acc, row=R[l], pair="rope", cos_sin=cs[l], cos_sin_period=P)
+        assert pc.compare_bf16(oracle, outs[0][1][l], want2)[0] == 0
