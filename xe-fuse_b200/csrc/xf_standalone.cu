@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(1024) rstd_quant_smem_kernel(const __nv_bfloat
           uint32_t packed = 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            float qv = roundf(__fdividef(f[k] * rstd, scale));   // half away from zero
+            float qv = roundf(__fdiv_rn(f[k] * rstd, scale));   // the reference's exact quotient, half away from zero
             qv = fminf(fmaxf(qv, -128.0f), 127.0f);
             packed |= (static_cast<uint32_t>(static_cast<int>(qv)) & 0xFFu) << (8 * k);
           }
@@ -368,9 +368,15 @@ __global__ void __launch_bounds__(1024) rstd_quant_smem_kernel(const __nv_bfloat
 // vectors (8 bf16 each) of the row, the sum of squares and the absolute maximum are reduced
 // together (max|x * rstd| == max|x| * rstd: rounding is monotone and rstd > 0), and the int8 row is
 // written from the registers.  One HBM read, one write, two block-wide reductions per row; the
-// next row a block will take is loaded before the current one is processed.  Rounding half away
-// from zero uses full-rate instructions only: q + 1.5 * 2^23 leaves round-to-nearest-even(q) in the
-// low mantissa bits, and an exact tie (q = k + 0.5, rare) is redone on q +- 0.5, an integer.
+// next row a block will take is loaded before the current one is processed.  Rounding uses
+// full-rate instructions only: q + 1.5 * 2^23 leaves round-to-nearest-even(q) in the low mantissa
+// bits, and a value within 1e-4 of a tie k + 0.5 (rare) is redone with the exact quotient.
+// The reference's quantised value, round(normed / scale) with the exact quotient; out of line so the
+// rare elements that need it do not cost the common path registers.
+__device__ __forceinline__ float exact_quotient_rounded(float normed, float scale) {
+  return roundf(__fdiv_rn(normed, scale));
+}
+
 template <int VPT>
 __global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16* __restrict__ x,
                                                              float* __restrict__ scale_out,
@@ -416,8 +422,13 @@ __global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16
         const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
         // |x * rstd| <= amax * rstd < 127 * scale, so q stays inside [-127.5, 127.5]: no clamp needed
         const float kMagic = 12582912.0f;   // 1.5 * 2^23: q + kMagic holds rne(q) in its low bits
+        // q = (x * rstd) * (1 / scale) is within 1.5e-5 of the reference's (x * rstd) / scale (|q| < 128), which
+        // decides the rounded value except within that distance of k + 0.5: those few are redone with
+        // the exact quotient and rounded half away from zero, so the int8 values equal the
+        // reference's whenever rstd does.
+        const float kTieWindow = 0.49998f;   // 0.5 - 2e-5: beyond twice the error bound of the product
         float q[8], m[8];
-        bool tie = false;
+        bool near_tie = false;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           q[2 * t] = (__uint_as_float(w[t] << 16) * rstd) * inv_scale;
@@ -426,12 +437,16 @@ __global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           m[e] = q[e] + kMagic;
-          tie |= fabsf(q[e] - (m[e] - kMagic)) == 0.5f;
+          near_tie |= fabsf(q[e] - (m[e] - kMagic)) > kTieWindow;
         }
-        if (tie) {   // an exact k + 0.5 somewhere in these 8: round those away from zero
+        if (near_tie) {
 #pragma unroll
           for (int e = 0; e < 8; ++e)
-            if (fabsf(q[e] - (m[e] - kMagic)) == 0.5f) m[e] = (q[e] + copysignf(0.5f, q[e])) + kMagic;
+            if (fabsf(q[e] - (m[e] - kMagic)) > kTieWindow) {
+              const uint32_t we = w[e >> 1];
+              const float xe = (e & 1) ? __uint_as_float(we & 0xFFFF0000u) : __uint_as_float(we << 16);
+              m[e] = exact_quotient_rounded(xe * rstd, scale) + kMagic;
+            }
         }
         uint32_t o[2] = {0u, 0u};
 #pragma unroll
