@@ -280,6 +280,54 @@ def test_tail_operand_staging_is_bit_identical(preset, shape, capi, oracle, cuda
     assert pc.compare_bf16(oracle, got_a, want)[0] == 0
 
 
+@pytest.mark.parametrize("preset,shape,extra", [
+    ("k0a", (384, 768, 512), 0),
+    ("k0a", (200, 336, 208), 0),               # ragged rows and columns: boxes past the edges read as zero
+    ("k0a", (2048, 4096, 512), 0),             # several tiles per CTA: staged last tile + TMA slices before it
+    ("k0a", (2048, 4096, 512), "no_tail"),     # every tile through the per-slice TMA loads
+    ("k0_dual", (384, 768, 512), 0),           # residual + aux store
+    ("k0a", (512, 4096, 4096), 0),             # cluster split-K variant (partials from the partner pair)
+    ("k0a", (640, 2304, 8192), 0),             # remainder wave split along K (partials from the workspace)
+])
+def test_residual_through_tma_is_bit_identical(preset, shape, extra, capi, oracle, cuda):
+    """The residual of a 32-column slice comes by TMA into the buffer its result is stored from
+    (default) or through per-thread 16-byte loads (XF_FLAG_NO_RESIDUAL_TMA): same bits out."""
+    M, N, K = shape
+    base = capi.FLAG_NO_TAIL_STAGING if extra == "no_tail" else 0
+    d = pc.make_inputs(oracle, preset, M, N, K, seed=5)
+    plan_a, got_a, aux_a = run_gpu(capi, oracle, preset, d, cuda, flags=base)
+    plan_b, got_b, aux_b = run_gpu(capi, oracle, preset, d, cuda, flags=base | capi.FLAG_NO_RESIDUAL_TMA)
+    assert plan_a.device_status() == 0 and plan_b.device_status() == 0
+    assert np.array_equal(got_a, got_b), plan_a.kernel_name
+    if aux_a is not None:
+        assert np.array_equal(aux_a, aux_b)
+    _, want = pc.expected(oracle, preset, d)
+    if isinstance(want, tuple):
+        want = want[0]
+    assert pc.compare_bf16(oracle, got_a, want)[0] == 0
+
+
+def test_residual_through_tma_in_place(capi, oracle, cuda):
+    """D aliases the residual (x += A @ B, the reference's O-projection use): a slice's residual is
+    read before the same slice is stored, whichever way it is fetched."""
+    import torch
+    from conftest import bf16_bits
+    M, N, K = 1024, 2048, 512
+    rng = np.random.default_rng(23)
+    A = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    B = oracle.f32_to_bf16((rng.standard_normal((K, N)) * K ** -0.5).astype(np.float32))
+    res = oracle.f32_to_bf16(rng.standard_normal((M, N)).astype(np.float32))
+    want = oracle.epilogue(oracle.gemm_bf16(A, B), residual=res)
+    tA, tB = _t(torch, A, cuda, True), _t(torch, B, cuda, True)
+    for flags in (0, capi.FLAG_NO_RESIDUAL_TMA):
+        X = _t(torch, res, cuda, True).clone()
+        plan = capi.GemmPlan(tA, tB, X, residual=X, flags=flags)
+        plan.run()
+        torch.cuda.synchronize()
+        assert plan.device_status() == 0
+        assert pc.compare_bf16(oracle, bf16_bits(X), want)[0] == 0
+
+
 def test_batched_full_matrix_operands(capi, oracle, cuda):
     """L > 1 with a residual (batch stride M*N) and with a per-head RoPE table (batch stride M*P):
     the staged operand of the last tile takes its batch from the tile's batch index."""

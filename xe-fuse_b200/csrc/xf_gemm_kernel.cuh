@@ -576,6 +576,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* xfree_bar = bars + 2 * STAGES + 7;   // [1]  KC>1: the other K groups' stages are idle
   uint64_t* xdata_bar = bars + 2 * STAGES + 8;   // [1]  KC>1: their partial accumulators have landed
   uint64_t* opnd_bar = bars + 2 * STAGES + 9;    // [1]  the last tile's staged epilogue operand has landed
+  uint64_t* res_bar = bars + 2 * STAGES + 10;    // [12 warps][2]  a warp's residual slice has landed in its staging buffer
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -613,6 +614,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         ptx::mbar_init(ptx::smem_u32(xfree_bar), KC > 1 ? KC - 1 : 1);
         ptx::mbar_init(ptx::smem_u32(xdata_bar), KC > 1 ? (KC - 1) * xchg_warps * 32 : 1);
         ptx::mbar_init(ptx::smem_u32(opnd_bar), 1);
+        for (int i = 0; i < 2 * (C::EPI_WARPS + 4); ++i) ptx::mbar_init(ptx::smem_u32(&res_bar[i]), 1);
       }
       ptx::mbar_init(ptx::smem_u32(&tempty_bar[b]), C::EPI_WARPS * CTAS);
     }
@@ -812,6 +814,8 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     uint8_t* stg = helper ? stage_base + warp * (C::EPI_BUFS * C::EPI_BUF_BYTES)
                           : epi_base + ew * (C::EPI_BUFS * C::EPI_BUF_BYTES);
     int sidx = 0;
+    uint32_t res_phase = 0;                 // parity bits of this warp's two residual-slice barriers
+    bool res_failed = false;
     int kb_seen = 0;                        // K blocks this CTA's pipeline has carried so far
     const uint8_t* staged = nullptr;        // the last tile's operand tile in shared memory, if staged
     const bool compact = e.compact != 0;
@@ -1002,6 +1006,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       // memory) it receives the NEXT accumulator slice of this warp while the current one is being
       // processed, so the TMEM read latency is paid once per tile instead of once per slice.
       uint4 pre[8];
+      // residual slices by TMA into the buffer the result will be stored from (bf16 TMA-store path only)
+      const bool res_by_tma = p.res_tma != 0 && pre_which == PRE_RESIDUAL && !use_staged && !compact &&
+                              !p.direct_store && p.d_dtype == DT_BF16 && warp_rows_ok && !(p.diag & (4 | 8));
       const bool acc_prefetch = part_base == nullptr && (pre_which == PRE_NONE || use_staged) && !(p.diag & 32);
       bool prefetched = false;
       for (int u = u_first; u < u_end; u += u_step) {
@@ -1018,7 +1025,16 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
           const int tcol0 = s * 32;
           // the residual / cos_sin loads of this slice go out before the accumulator is read
           int pre_mode = 0;
-          if (!acc_prefetch && !use_staged && row_ok && !(p.diag & 4) && p.d_dtype != DT_S32) {
+          if (res_by_tma) {
+            // the buffer this slice's store will use: free once the store of two slices ago has read it
+            if (lane == 0) {
+              ptx::tma_store_wait_read<C::EPI_BUFS - 1>();
+              const uint32_t rb = ptx::smem_u32(&res_bar[warp * 2 + sidx]);
+              ptx::mbar_arrive_expect_tx(rb, C::EPI_BUF_BYTES);
+              ptx::tma_load_3d<1>(ptx::smem_u32(stg + sidx * C::EPI_BUF_BYTES), &p.tm_res, rb, n0 + tcol0,
+                                  m0 + q * 32, l);
+            }
+          } else if (!acc_prefetch && !use_staged && row_ok && !(p.diag & 4) && p.d_dtype != DT_S32) {
             if (pre_which == PRE_RESIDUAL)
               pre_mode = mat_row32_issue(e.residual, l, row, n0 + tcol0, p.N, pre);
             else if (pre_which == PRE_COS_SIN)
@@ -1124,6 +1140,19 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             }
             stored_direct = true;
             continue;
+          }
+          if (res_by_tma) {
+            const uint32_t rb = ptx::smem_u32(&res_bar[warp * 2 + sidx]);
+            if (!ptx::mbar_wait(rb, (res_phase >> sidx) & 1u, budget)) {
+              if (p.status && lane == 0) atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_EPI_OPERAND);
+              res_failed = true;
+            }
+            res_phase ^= 1u << sidx;
+            const uint8_t* sb = stg + sidx * C::EPI_BUF_BYTES + lane * 64;
+            const int sw = (lane >> 1) & 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pre[j] = *reinterpret_cast<const uint4*>(sb + ((j ^ sw) << 4));
+            pre_mode = 1;
           }
           epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs, pre_which, pre_mode, pre,
                                use_staged ? staged : nullptr, q * 32 + lane,

@@ -62,6 +62,10 @@ struct alignas(64) GemmParams {
   // while that tile's main loop drains (tail_opnd != 0): residual bf16 [L][M][N], box {64 cols,
   // 128 rows}; or the per-head cos_sin table fp32 [L][M][P], box {32 cols, 128 rows}; 128-B swizzle.
   CUtensorMap tm_opnd;
+  // The residual again, box {32 columns, 32 rows}, 64-B swizzle: the geometry of a D store.  With
+  // res_tma != 0 an epilogue warp TMA-loads the residual of a 32-column slice into the staging
+  // buffer its result will leave from, reads its rows there and overwrites them with the result.
+  CUtensorMap tm_res;
   int M, N, K, L;
   int tiles_m, tiles_n;    // in units of the cluster tile (128*CTAS rows x BN columns)
   int num_kb;              // ceil(K / KBLK)
@@ -77,6 +81,7 @@ struct alignas(64) GemmParams {
   int direct_store;        // 1: plain global stores for D
   int tail_opnd;           // 0 none, 1 residual, 2 cos_sin table: what tm_opnd describes
   int tail_opnd_boxes;     // boxes of 16 KB that make up one CTA tile of that operand
+  int res_tma;             // 1: residual slices come through tm_res instead of per-thread global loads
   int diag;                // diagnostics: bit0 skip the TMA loads, bit1 skip the MMAs (results are garbage)
   int* status;             // device status word (may be null)
   // Split-K of the remainder wave: work items [0, split_first) are whole tiles; the tiles from
