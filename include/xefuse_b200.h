@@ -201,9 +201,10 @@ typedef struct xf_gemm_desc {
 #define XF_FLAG_NO_ACC_PREFETCH 524288 /* the epilogue reads each 32-column accumulator slice out of tensor
                                     memory when it needs it (by default a warp requests its next slice
                                     while it works on the current one, where it has registers to spare) */
-#define XF_FLAG_NO_RESIDUAL_TMA 2097152 /* the epilogue reads the residual with per-thread 16-byte loads (by
-                                    default TMA brings each 32 x 32 residual block into the staging
-                                    buffer its result is then stored from) */
+#define XF_FLAG_NO_RESIDUAL_TMA 2097152 /* the epilogue reads the residual with per-thread 16-byte loads and
+                                    writes the auxiliary output with per-thread stores (by default TMA
+                                    brings each 32 x 32 residual block into the staging buffer its result
+                                    is then stored from, and the auxiliary block leaves the same way) */
 #define XF_FLAG_FORCE_CLUSTER_SPLIT 131072 /* use a cluster split-K variant whenever K is long enough, also
                                     for problems with more tiles than co-resident clusters */
 

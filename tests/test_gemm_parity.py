@@ -307,6 +307,44 @@ def test_residual_through_tma_is_bit_identical(preset, shape, extra, capi, oracl
     assert pc.compare_bf16(oracle, got_a, want)[0] == 0
 
 
+@pytest.mark.parametrize("shape,with_residual,L", [
+    ((384, 768, 512), True, 1),
+    ((200, 336, 208), True, 1),          # ragged: the TMA store clips rows beyond M and columns beyond N
+    ((2048, 4096, 512), True, 1),        # several tiles per CTA
+    ((1024, 2048, 256), False, 1),       # auxiliary output of the bare accumulator
+    ((200, 384, 160), True, 3),          # batched
+])
+def test_aux_store_through_tma_is_bit_identical(shape, with_residual, L, capi, oracle, cuda):
+    """The second (auxiliary) output leaves through a staging buffer and a TMA store (default) or
+    through per-thread stores (XF_FLAG_NO_RESIDUAL_TMA): same bits in D and in the auxiliary tensor."""
+    import torch
+    from conftest import bf16_bits
+    M, N, K = shape
+    rng = np.random.default_rng(29)
+    A = oracle.f32_to_bf16(rng.standard_normal((L, M, K)).astype(np.float32))
+    B = oracle.f32_to_bf16((rng.standard_normal((L, K, N)) * K ** -0.5).astype(np.float32))
+    res = oracle.f32_to_bf16(rng.standard_normal((L, M, N)).astype(np.float32))
+    gamma = rng.normal(1.0, 0.02, (L, N)).astype(np.float32)
+    tA, tB = _t(torch, A, cuda, True), _t(torch, B, cuda, True)
+    outs = {}
+    for flags in (0, capi.FLAG_NO_RESIDUAL_TMA):
+        D = torch.full((L, M, N), float("nan"), dtype=torch.bfloat16, device=cuda)
+        aux = torch.full((L, M, N), float("nan"), dtype=torch.bfloat16, device=cuda)
+        plan = capi.GemmPlan(tA, tB, D, residual=_t(torch, res, cuda, True) if with_residual else None, aux_store=aux,
+                             col_scale=_t(torch, gamma.reshape(-1), cuda), flags=flags)
+        plan.run()
+        torch.cuda.synchronize()
+        assert plan.device_status() == 0
+        outs[flags] = (bf16_bits(D).copy(), bf16_bits(aux).copy())
+    assert np.array_equal(outs[0][0], outs[capi.FLAG_NO_RESIDUAL_TMA][0])
+    assert np.array_equal(outs[0][1], outs[capi.FLAG_NO_RESIDUAL_TMA][1])
+    for l in range(L):
+        acc = oracle.gemm_bf16(A[l], B[l])
+        want, want_aux = oracle.epilogue(acc, residual=res[l] if with_residual else None, col=gamma[l], want_aux=True)
+        assert pc.compare_bf16(oracle, outs[0][0][l], want)[0] == 0
+        assert pc.compare_bf16(oracle, outs[0][1][l], want_aux)[0] == 0
+
+
 def test_residual_through_tma_in_place(capi, oracle, cuda):
     """D aliases the residual (x += A @ B, the reference's O-projection use): a slice's residual is
     read before the same slice is stored, whichever way it is fetched."""

@@ -683,6 +683,18 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
         p.res_tma = 1;
     }
   }
+  p.aux_tma = 0;
+  if (e.aux_store.enabled && !p.direct_store && !p.epi.compact && !(d->flags & XF_FLAG_NO_RESIDUAL_TMA)) {
+    const xf_mat& m = e.aux_store;
+    const bool multi = d->L > 1;
+    if (m.dtype == XF_DT_BF16 && aligned16(m.ptr) && (m.ld * 2) % 16 == 0 &&
+        (!multi || (m.batch_stride > 0 && (m.batch_stride * 2) % 16 == 0))) {
+      const uint64_t s2 = multi ? (uint64_t)m.batch_stride * 2 : (uint64_t)m.ld * 2 * d->M;
+      if (encode_3d(&p.tm_aux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, m.ptr, d->N, d->M, d->L, (uint64_t)m.ld * 2, s2,
+                    32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+        p.aux_tma = 1;
+    }
+  }
   p.num_d_peer = d->num_d_peer;
   for (int c = 0; c < d->num_d_peer; ++c) {
     p.D_peer[c] = d->D_peer[c];

@@ -414,6 +414,9 @@ __device__ __forceinline__ void store_bf16_row(__nv_bfloat16* ptr, const uint32_
 //   staged / srow / scol   the operand tile TMA staged in shared memory for a CTA's last tile (or
 //          null), this thread's row in it and the first of the 32 columns; it takes the place of
 //          `pre`, whose registers then carry the next accumulator slice
+//   aux_row / aux_sw   non-null: the auxiliary output of this row goes to these 64 bytes of a
+//          64-byte-swizzled staging buffer (16-byte chunk j at (j ^ aux_sw)) and the caller stores
+//          the buffer with TMA; null: the thread stores its row to global memory itself
 __device__ __forceinline__ void rope_pair(float xe, float xo, float c, float s, float& oe, float& oo) {
   oe = xe * c + xo * s;
   oo = -xe * s + xo * c;
@@ -424,7 +427,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
                                                float (&v)[32], int row, bool row_ok, int l,
                                                int gcol0, float rs, int pre_which, int pre_mode,
                                                const uint4 (&pre)[8], const uint8_t* staged, int srow,
-                                               int scol) {
+                                               int scol, uint8_t* aux_row = nullptr, int aux_sw = 0) {
 #pragma unroll
   for (int i = 0; i < 32; ++i)
     v[i] = (KIND == 0) ? __uint_as_float(r[i]) : static_cast<float>(static_cast<int>(r[i]));
@@ -465,10 +468,17 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-    __nv_bfloat16* ptr = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(e.aux_store.ptr)) +
-                         static_cast<long long>(l) * e.aux_store.batch_stride +
-                         static_cast<long long>(row) * e.aux_store.ld + gcol0;
-    store_bf16_row(ptr, pk, N - gcol0, 32);
+    if (aux_row != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(aux_row + ((j ^ aux_sw) << 4)) =
+            make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    } else {
+      __nv_bfloat16* ptr = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(e.aux_store.ptr)) +
+                           static_cast<long long>(l) * e.aux_store.batch_stride +
+                           static_cast<long long>(row) * e.aux_store.ld + gcol0;
+      store_bf16_row(ptr, pk, N - gcol0, 32);
+    }
   }
   if (e.row_scale.enabled) {
 #pragma unroll
@@ -1009,6 +1019,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       // residual slices by TMA into the buffer the result will be stored from (bf16 TMA-store path only)
       const bool res_by_tma = p.res_tma != 0 && pre_which == PRE_RESIDUAL && !use_staged && !compact &&
                               !p.direct_store && p.d_dtype == DT_BF16 && warp_rows_ok && !(p.diag & (4 | 8));
+      // the auxiliary output through a staging buffer and a TMA store (same conditions as the D store)
+      const bool aux_by_tma = p.aux_tma != 0 && !compact && !p.direct_store && p.d_dtype == DT_BF16 &&
+                              warp_rows_ok && !(p.diag & (4 | 8));
       const bool acc_prefetch = part_base == nullptr && (pre_which == PRE_NONE || use_staged) && !(p.diag & 32);
       bool prefetched = false;
       for (int u = u_first; u < u_end; u += u_step) {
@@ -1154,9 +1167,25 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             for (int j = 0; j < 4; ++j) pre[j] = *reinterpret_cast<const uint4*>(sb + ((j ^ sw) << 4));
             pre_mode = 1;
           }
+          if (aux_by_tma && !res_by_tma) {   // the buffer the auxiliary block leaves from must be free
+            if (lane == 0) ptx::tma_store_wait_read<C::EPI_BUFS - 1>();
+            __syncwarp();
+          }
           epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs, pre_which, pre_mode, pre,
                                use_staged ? staged : nullptr, q * 32 + lane,
-                               pre_which == PRE_RESIDUAL ? tcol0 : cos_sin_col(e, n0 + tcol0));
+                               pre_which == PRE_RESIDUAL ? tcol0 : cos_sin_col(e, n0 + tcol0),
+                               aux_by_tma ? stg + sidx * C::EPI_BUF_BYTES + lane * 64 : nullptr, (lane >> 1) & 3);
+          if (aux_by_tma) {
+            // (with the residual fetched by TMA this is the buffer it arrived in: every lane has read
+            // its row and overwritten it with the auxiliary values)
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_3d(&p.tm_aux, ptx::smem_u32(stg + sidx * C::EPI_BUF_BYTES), n0 + tcol0, m0 + q * 32, l);
+              ptx::tma_store_commit();
+            }
+            sidx = (sidx + 1 == C::EPI_BUFS) ? 0 : sidx + 1;
+          }
           if (e.row_sumsq != nullptr) {
             // side output for a following RMSNorm: this row's sum of squares over these 32 columns
             const int nv = p.N - (n0 + tcol0);

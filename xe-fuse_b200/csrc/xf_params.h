@@ -66,6 +66,9 @@ struct alignas(64) GemmParams {
   // res_tma != 0 an epilogue warp TMA-loads the residual of a 32-column slice into the staging
   // buffer its result will leave from, reads its rows there and overwrites them with the result.
   CUtensorMap tm_res;
+  // The auxiliary output (acc + residual, bf16 [M,N]) with the geometry of a D store; with
+  // aux_tma != 0 a warp's 32 x 32 block of it leaves through a staging buffer and a TMA store.
+  CUtensorMap tm_aux;
   int M, N, K, L;
   int tiles_m, tiles_n;    // in units of the cluster tile (128*CTAS rows x BN columns)
   int num_kb;              // ceil(K / KBLK)
@@ -82,6 +85,7 @@ struct alignas(64) GemmParams {
   int tail_opnd;           // 0 none, 1 residual, 2 cos_sin table: what tm_opnd describes
   int tail_opnd_boxes;     // boxes of 16 KB that make up one CTA tile of that operand
   int res_tma;             // 1: residual slices come through tm_res instead of per-thread global loads
+  int aux_tma;             // 1: the auxiliary output leaves through tm_aux instead of per-thread stores
   int diag;                // diagnostics: bit0 skip the TMA loads, bit1 skip the MMAs (results are garbage)
   int* status;             // device status word (may be null)
   // Split-K of the remainder wave: work items [0, split_first) are whole tiles; the tiles from
