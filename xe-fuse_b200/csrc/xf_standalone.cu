@@ -377,12 +377,27 @@ __device__ __forceinline__ float exact_quotient_rounded(float normed, float scal
   return roundf(__fdiv_rn(normed, scale));
 }
 
+// Sum and maximum over the block with one pair of barriers.
+__device__ __forceinline__ void block_reduce_sum_max(float& s, float& m, float2* red) {
+  s = warp_sum(s);
+  m = warp_max(m);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = make_float2(s, m);
+  __syncthreads();
+  const float2 r = (l < nw) ? red[l] : make_float2(0.0f, 0.0f);
+  s = warp_sum(r.x);
+  m = warp_max(r.y);
+}
+
+// Up to 4 vectors per thread run in blocks of at most 256 threads, four of them per SM (64
+// registers): the kernel is bound by instruction issue and by the two barriers per row, and a
+// fourth resident block hides more of both than the registers it costs.
 template <int VPT>
-__global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16* __restrict__ x,
-                                                             float* __restrict__ scale_out,
-                                                             int8_t* __restrict__ xq, long long rows,
-                                                             int N, float eps) {
-  __shared__ float red[32];
+__global__ void __launch_bounds__(VPT < 8 ? 256 : 512, VPT < 8 ? 4 : 1)
+rstd_quant_reg_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ scale_out,
+                      int8_t* __restrict__ xq, long long rows, int N, float eps) {
+  __shared__ float2 red[32];
   const int nvec = N / 8;
   auto load_row = [&](uint4 (&dst)[VPT], long long row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * N);
@@ -409,8 +424,7 @@ __global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16
         amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
       }
     }
-    ss = block_reduce<false>(ss, red);
-    amax = block_reduce<true>(amax, red);
+    block_reduce_sum_max(ss, amax, red);
     const float rstd = 1.0f / sqrtf(ss / static_cast<float>(N) + eps);
     const float scale = (amax * rstd) / 127.0f + 1e-8f;
     const float inv_scale = 1.0f / scale;   // one division per row; the elements multiply
@@ -421,7 +435,7 @@ __global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16
       if (i < nvec) {
         const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
         // |x * rstd| <= amax * rstd < 127 * scale, so q stays inside [-127.5, 127.5]: no clamp needed
-        const float kMagic = 12582912.0f;   // 1.5 * 2^23: q + kMagic holds rne(q) in its low bits
+        const float kMagic = 12582912.0f;   // 1.5 * 2^23: q + kMagic holds rne(q) in its low mantissa bits
         // q = (x * rstd) * (1 / scale) is within 1.5e-5 of the reference's (x * rstd) / scale (|q| < 128), which
         // decides the rounded value except within that distance of k + 0.5: those few are redone with
         // the exact quotient and rounded half away from zero, so the int8 values equal the
@@ -448,10 +462,15 @@ __global__ void __launch_bounds__(512) rstd_quant_reg_kernel(const __nv_bfloat16
               m[e] = exact_quotient_rounded(xe * rstd, scale) + kMagic;
             }
         }
-        uint32_t o[2] = {0u, 0u};
+        // the low byte of (integer + kMagic)'s bit pattern is the integer's two's-complement byte:
+        // three byte permutes gather four of them
+        uint32_t o[2];
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          o[e >> 2] |= (static_cast<uint32_t>(__float_as_int(m[e]) - 0x4B400000) & 0xFFu) << (8 * (e & 3));
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t lo = __byte_perm(__float_as_uint(m[4 * h]), __float_as_uint(m[4 * h + 1]), 0x0040);
+          const uint32_t hi = __byte_perm(__float_as_uint(m[4 * h + 2]), __float_as_uint(m[4 * h + 3]), 0x0040);
+          o[h] = __byte_perm(lo, hi, 0x5410);
+        }
         qr[i] = make_uint2(o[0], o[1]);
       }
     }
