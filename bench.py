@@ -458,6 +458,24 @@ class Workload:
         self.check_status()
         return self.flops_total * steps / (ms * 1e-3) / 1e12, ms / steps
 
+    def step_times(self, steps):
+        """A separate pass of `steps` steps with an event pair around EACH step (max over ranks per
+        step): best and median ms per step, as the reference's harnesses print them."""
+        torch = self.torch
+        self.ctx["barrier"]()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record()
+        for i in range(steps):
+            self.step()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(steps)], device=self.ctx["dev"])
+        if self.ctx["dist"] is not None:
+            self.ctx["dist"].all_reduce(t, op=self.ctx["dist"].ReduceOp.MAX)
+        t = sorted(t.tolist())
+        return {"best_ms": t[0], "median_ms": t[len(t) // 2], "worst_ms": t[-1], "n": steps,
+                "how": "one CUDA-event pair per step in a pass of its own, max over ranks per step"}
+
     def sustained(self, ms_per_step, seconds=0.5, min_steps=0):
         """The same step back to back for about `seconds`: (TFLOP/s, ms per step, wall window)."""
         barrier = self.ctx["barrier"]
@@ -842,6 +860,34 @@ def cpu_sample(stages, seconds_target, seed):
     return fl / t / 1e12, rows, t, cores, [p[2] for p in plans]
 
 
+def cpu_library_gemm(stages, seconds_target=3.0):
+    """The best CPU GEMM at hand for context: torch.matmul (oneDNN/MKL) on the same host cores, on
+    the first stage's K and up to 4096 of its columns, GEMM only (no epilogue)."""
+    import torch
+    (_, M, N, K, dt) = stages[0][:5]
+    torch.set_num_threads(cpu_threads())
+    Nc, r = min(N, 4096), min(M, 1024)
+    if dt == "bf16":
+        A = torch.randn(r, K).to(torch.bfloat16)
+        B = torch.randn(K, Nc).to(torch.bfloat16)
+        fn, what = (lambda: torch.matmul(A, B)), "torch.matmul bf16"
+    else:
+        A = torch.randint(-127, 128, (r, K), dtype=torch.int8)
+        B = torch.randint(-127, 128, (K, Nc), dtype=torch.int8)
+        fn, what = (lambda: torch._int_mm(A, B)), "torch._int_mm int8"
+    try:
+        fn()
+        n, t0 = 0, time.perf_counter()
+        while n < 2 or (time.perf_counter() - t0 < seconds_target and n < 200):
+            fn()
+            n += 1
+        t = (time.perf_counter() - t0) / n
+    except Exception as e:        # a CPU build without that kernel: report it, the oracle figure stands
+        return {"unavailable": f"{what} on CPU: {type(e).__name__}"}
+    return {"value": 2.0 * r * Nc * K / t / 1e12, "unit": "TOP/s" if dt != "bf16" else "TFLOP/s",
+            "what": f"{what}, {r} x {Nc} x {K}, GEMM only, {torch.get_num_threads()} threads"}
+
+
 def run_reference_arm(args, stages):
     """`--impl reference`: the reference's path on the host cores.  The reference itself is SYCL
     for Intel Xe with no host implementation, so this is the CPU oracle (a port of its formulas),
@@ -955,6 +1001,7 @@ def main():
     # value_sustained, and the SM clock is read over that window; throttle reasons are collected
     # over the whole run.
     value, ms_per_step = wl.timed(args.steps, args.warmup)
+    step_times = wl.step_times(args.steps)
     v_sus, ms_sus, load_window, n_sus = wl.sustained(ms_per_step, min_steps=args.steps)
     sm_sus, _ = sampler.median_sm(*load_window)
 
@@ -1031,7 +1078,8 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         v, rows, t, cores, cols = cpu_sample(stages, args.cpu_seconds, seed=0)
         cpu_baseline = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                        "sample": f"{rows} rows x {cols} columns x full K of the workload, {t:.1f} s of CPU time"}
+                        "sample": f"{rows} rows x {cols} columns x full K of the workload, {t:.1f} s of CPU time",
+                        "library_gemm": cpu_library_gemm(stages)}
 
     sus_den = peaks.get("bf16_sustained")
     value_sustained = {
@@ -1053,6 +1101,7 @@ def main():
                                    if world > 1 and has_chain else "")),
                    "l2": l2_note, "kernels": kernels},
         "value_sustained": value_sustained,
+        "step_times": step_times,
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "unfused": unfused,
         "gpu_launches": args.steps * n_stage, "clocks": clocks,
     }
