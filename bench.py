@@ -854,8 +854,15 @@ def cpu_sample(stages, seconds_target, seed):
             fl += 2.0 * r * Nc * K
         return t, fl
     t16, f16 = run(16)
-    rows = int(max(16, min(max(p[1] for p in plans), 16 * seconds_target / max(t16, 1e-3))))
+    m_max = max(p[1] for p in plans)
+    rows = int(max(16, min(m_max, 16 * seconds_target / max(t16, 1e-3))))
     rows = (rows // 4) * 4
+    # all rows fit the time target: widen the column sample too, up to the whole workload
+    t_rows = t16 * rows / 16.0
+    if rows >= m_max and t_rows < seconds_target:
+        grow = seconds_target / max(t_rows, 1e-3)
+        plans = [(preset, M, int(min(N, max(Nc, (int(Nc * grow) // 256) * 256))), K, dt)
+                 for (preset, M, Nc, K, dt), N in zip(plans, [st[2] for st in stages])]
     t, fl = run(rows)
     return fl / t / 1e12, rows, t, cores, [p[2] for p in plans]
 
@@ -896,7 +903,7 @@ def run_reference_arm(args, stages):
     if rank != 0:
         return
     steps, warm = args.steps, args.warmup
-    per_step = max(0.5, min(4.0, 120.0 / max(1, steps + warm)))
+    per_step = max(0.5, min(6.0, 150.0 / max(1, steps + warm)))
     vals = []
     rows = cores = None
     cols = None
