@@ -205,6 +205,9 @@ typedef struct xf_gemm_desc {
                                     writes the auxiliary output with per-thread stores (by default TMA
                                     brings each 32 x 32 residual block into the staging buffer its result
                                     is then stored from, and the auxiliary block leaves the same way) */
+#define XF_FLAG_GENERIC_EPILOGUE 4194304 /* launch the kernel instance that carries every epilogue step (by
+                                    default a plan launches the instance compiled for the smallest class
+                                    of steps that covers its descriptor; same results, shorter tail) */
 #define XF_FLAG_FORCE_CLUSTER_SPLIT 131072 /* use a cluster split-K variant whenever K is long enough, also
                                     for problems with more tiles than co-resident clusters */
 

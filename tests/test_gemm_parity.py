@@ -345,6 +345,26 @@ def test_aux_store_through_tma_is_bit_identical(shape, with_residual, L, capi, o
         assert pc.compare_bf16(oracle, outs[0][1][l], want_aux)[0] == 0
 
 
+@pytest.mark.parametrize("preset", pc.PRESETS)
+@pytest.mark.parametrize("shape", [(384, 768, 512), (200, 336, 208), (2048, 2048, 256)],
+                         ids=["aligned", "ragged", "several_tiles"])
+def test_class_instance_matches_the_generic_one(preset, shape, capi, oracle, cuda):
+    """A plan launches the kernel instance compiled for its epilogue class (scales only, residual,
+    GLU pair, RoPE, or everything); XF_FLAG_GENERIC_EPILOGUE forces the all-in-one instance.  Same
+    bits out for every preset, aligned, ragged and with several tiles per CTA."""
+    M, N, K = shape
+    if pc.is_int8(preset) and (N % 16 or K % 16):
+        N, K = 352, 208
+    if preset == "k4v2_table" and N % 128:
+        N = 384           # whole 128-column heads for the per-head table
+    d = pc.make_inputs(oracle, preset, M, N, K, seed=11)
+    plan_a, got_a, aux_a = run_gpu(capi, oracle, preset, d, cuda)
+    plan_b, got_b, aux_b = run_gpu(capi, oracle, preset, d, cuda, flags=capi.FLAG_GENERIC_EPILOGUE)
+    assert np.array_equal(got_a, got_b), (preset, plan_a.kernel_name)
+    if aux_a is not None:
+        assert np.array_equal(aux_a, aux_b)
+
+
 def test_residual_through_tma_in_place(capi, oracle, cuda):
     """D aliases the residual (x += A @ B, the reference's O-projection use): a slice's residual is
     read before the same slice is stored, whichever way it is fetched."""

@@ -14,7 +14,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libxefuse_b200.so")
-SOURCES = ["xf_gemm.cu", "xf_standalone.cu", "xf_rowops.cu", "xf_harness.cu"]
+SOURCES = ["xf_gemm.cu", "xf_gemm_class_scale.cu", "xf_gemm_class_mat.cu", "xf_gemm_class_glu.cu",
+           "xf_gemm_class_rope.cu", "xf_gemm_class_all.cu", "xf_standalone.cu", "xf_rowops.cu", "xf_harness.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

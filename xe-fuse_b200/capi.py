@@ -25,6 +25,7 @@ FLAG_NO_CLUSTER_SPLIT, FLAG_FORCE_CLUSTER_SPLIT = 65536, 131072
 FLAG_NO_TAIL_STAGING = 262144
 FLAG_NO_ACC_PREFETCH = 524288
 FLAG_NO_RESIDUAL_TMA = 2097152
+FLAG_GENERIC_EPILOGUE = 4194304
 # timing diagnostics (D is garbage): honoured only with XEFUSE_ALLOW_DIAG=1 in the environment
 FLAG_DIAG_NO_LOAD, FLAG_DIAG_NO_MMA, FLAG_DIAG_NO_EPILOGUE, FLAG_DIAG_NO_STORE = 256, 512, 1024, 2048
 FLAG_DIAG_NO_ACC_READ = 1048576

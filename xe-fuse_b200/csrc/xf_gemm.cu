@@ -12,6 +12,7 @@
 #include "../../include/xefuse_b200.h"
 #include "xf_gemm_kernel.cuh"
 #include "xf_host_util.h"
+#include "xf_variants.h"
 
 namespace xf {
 
@@ -69,35 +70,24 @@ static bool encode_3d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base,
 }
 
 // ---------------------------------------------------------------------------- kernel table
-typedef void (*KernelFn)(const GemmParams);
-
+// A variant fixes the tile; each is compiled once per epilogue class (xf_variants.h), and a plan
+// launches the instance of the smallest class that covers its descriptor.
 struct Variant {
   int kind, bn, ctas, ks, kc, stages, smem;
-  KernelFn fn;
   const char* name;
 };
 
 #define XF_VARIANT(KIND, BN, CTAS, KS, KC, NAME)                                      \
   {KIND, BN, CTAS, KS, KC, TileCfg<KIND, BN, CTAS, KS, KC>::STAGES,                    \
-   TileCfg<KIND, BN, CTAS, KS, KC>::SMEM_BYTES, gemm_evt_kernel<KIND, BN, CTAS, KS, KC>, NAME}
+   TileCfg<KIND, BN, CTAS, KS, KC>::SMEM_BYTES, NAME},
 
-// name = <dtype>_<tile rows>x<columns>_cta<CTAs per MMA>_k<K elements per stage>[_kc<K groups per cluster>]
-static const Variant g_variants[] = {
-    XF_VARIANT(0, 256, 2, 1, 1, "bf16_256x256_cta2_k64"),
-    XF_VARIANT(0, 256, 2, 2, 1, "bf16_256x256_cta2_k128"),
-    XF_VARIANT(0, 256, 1, 1, 1, "bf16_128x256_cta1_k64"),
-    XF_VARIANT(0, 128, 2, 1, 1, "bf16_256x128_cta2_k64"),
-    XF_VARIANT(0, 128, 2, 2, 1, "bf16_256x128_cta2_k128"),
-    XF_VARIANT(0, 128, 1, 1, 1, "bf16_128x128_cta1_k64"),
-    XF_VARIANT(0, 128, 1, 2, 1, "bf16_128x128_cta1_k128"),
-    XF_VARIANT(0, 256, 2, 2, 2, "bf16_256x256_cta2_k128_kc2"),
-    XF_VARIANT(1, 256, 2, 1, 1, "s8_256x256_cta2_k128"),
-    XF_VARIANT(1, 256, 2, 2, 1, "s8_256x256_cta2_k256"),
-    XF_VARIANT(1, 256, 1, 1, 1, "s8_128x256_cta1_k128"),
-    XF_VARIANT(1, 128, 1, 1, 1, "s8_128x128_cta1_k128"),
-    XF_VARIANT(1, 128, 1, 2, 1, "s8_128x128_cta1_k256"),
-    XF_VARIANT(1, 256, 2, 2, 2, "s8_256x256_cta2_k256_kc2"),
-};
+static const Variant g_variants[] = {XF_FOR_EACH_VARIANT(XF_VARIANT)};
+#undef XF_VARIANT
+static const KernelFn* const g_class_tables[EC_COUNT] = {g_kernels_scale, g_kernels_mat, g_kernels_glu,
+                                                         g_kernels_rope, g_kernels_all};
+static KernelFn kernel_of(const Variant& v, int epi_class) {
+  return g_class_tables[epi_class][&v - g_variants];
+}
 static const int g_num_variants = sizeof(g_variants) / sizeof(g_variants[0]);
 
 }  // namespace xf
@@ -105,6 +95,7 @@ static const int g_num_variants = sizeof(g_variants) / sizeof(g_variants[0]);
 struct xf_plan {
   xf::GemmParams params;
   const xf::Variant* variant;
+  xf::KernelFn fn;         // the variant's instance for this plan's epilogue class
   int grid;
   int device;
   int no_pdl;   // 1: launch without programmatic stream serialization
@@ -427,8 +418,8 @@ struct Geometry {
 // Clusters of variant v the current device can hold at once (0 if the query fails).
 static int active_clusters_of(const Variant& v, int sm_count) {
   const int cl = v.ctas * v.kc;
-  if (cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           v.smem) != cudaSuccess) {
+  const void* fn = reinterpret_cast<const void*>(kernel_of(v, EC_ALL));   // every class has this footprint
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, v.smem) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -442,7 +433,7 @@ static int active_clusters_of(const Variant& v, int sm_count) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int nclusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&nclusters, reinterpret_cast<const void*>(v.fn), &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&nclusters, fn, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -483,11 +474,13 @@ static xf_status plan_geometry(const xf_gemm_desc* d, Geometry* g) {
     return XF_ERR_NOT_SUPPORTED;
   }
   g->v = v; g->dev = dev; g->sm_count = sm_count;
-  cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(v->fn),
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem);
-  if (ce != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(smem=%d) failed: %s", v->smem, cudaGetErrorString(ce));
-    return XF_ERR_INTERNAL;
+  for (int c = 0; c < EC_COUNT; ++c) {
+    cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel_of(*v, c)),
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem);
+    if (ce != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(smem=%d) failed: %s", v->smem, cudaGetErrorString(ce));
+      return XF_ERR_INTERNAL;
+    }
   }
   const int es = elem_size(d->dtype_ab);
   g->num_kb = ceil_div(d->K, (128 / es) * v->ks);
@@ -616,6 +609,20 @@ static xf_status build_plan(const xf_gemm_desc* d, void* workspace, xf_plan* pla
            ((d->flags & XF_FLAG_DIAG_NO_EPILOGUE) ? 4 : 0) | ((d->flags & XF_FLAG_DIAG_NO_STORE) ? 8 : 0) |
            ((d->flags & XF_FLAG_NO_TAIL_HELP) ? 16 : 0) | ((d->flags & XF_FLAG_NO_ACC_PREFETCH) ? 32 : 0) |
            ((d->flags & XF_FLAG_DIAG_NO_ACC_READ) ? 64 : 0);
+  // The kernel instance: the smallest epilogue class that holds every step this descriptor uses.
+  {
+    int need = 0;
+    if (e.residual.enabled || e.aux_store.enabled) need |= EF_MAT;
+    if (e.unary != XF_UNARY_NONE) need |= EF_UNARY;
+    if (e.pair == XF_PAIR_SWIGLU || e.pair == XF_PAIR_GEGLU) need |= EF_GLU;
+    if (e.pair == XF_PAIR_ROPE) need |= EF_ROPE;
+    if ((e.pair != XF_PAIR_NONE && !(need & (EF_GLU | EF_ROPE))) || d->dtype_d != XF_DT_BF16 || p.direct_store ||
+        e.row_sumsq != nullptr)
+      need |= EF_MISC;
+    const int cls = need == 0 ? EC_SCALE : need == EF_MAT ? EC_MAT : need == EF_GLU ? EC_GLU
+                    : need == EF_ROPE ? EC_ROPE : EC_ALL;
+    plan->fn = kernel_of(*v, (d->flags & XF_FLAG_GENERIC_EPILOGUE) ? EC_ALL : cls);
+  }
 
   const CUtensorMapDataType dt =
       d->dtype_ab == XF_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
@@ -760,6 +767,8 @@ xf_status xf_gemm_workspace_size(const xf_gemm_desc* desc, size_t* bytes) {
   return XF_SUCCESS;
 }
 
+static xf_status static_workspace_address(void** out, int* dev_out);
+
 xf_status xf_gemm_plan_create(const xf_gemm_desc* desc, void* workspace, xf_plan** out) {
   if (!out) {
     xf::set_error("null plan output pointer");
@@ -778,6 +787,11 @@ xf_status xf_gemm_plan_create(const xf_gemm_desc* desc, void* workspace, xf_plan
     free(plan);
     return s;
   }
+  // The first plan on a device also looks up the static scratch array of the allocation-free entry,
+  // so that the module holding it is resident before that entry is ever called (the kernels live
+  // in modules of their own and are loaded when first launched).
+  void* unused = nullptr;
+  static_workspace_address(&unused, nullptr);
   *out = plan;
   return XF_SUCCESS;
 }
@@ -808,7 +822,7 @@ xf_status xf_gemm_run(xf_plan* plan, void* stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = plan->no_pdl ? 1 : 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, plan->variant->fn, plan->params);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, plan->fn, plan->params);
   if (e != cudaSuccess) {
     xf::set_error("launch of %s failed: %s", plan->name, cudaGetErrorString(e));
     return XF_ERR_INTERNAL;
@@ -836,7 +850,7 @@ static bool g_static_ws_ready[kMaxDevices];
 static std::mutex g_static_ws_mutex;
 
 // Device address of g_static_workspace on the CURRENT device; looked up once per device.
-static xf_status static_workspace_address(void** out, int* dev_out = nullptr) {
+static xf_status static_workspace_address(void** out, int* dev_out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) {
@@ -869,7 +883,7 @@ xf_status xf_gemm_run_static_workspace(const xf_gemm_desc* caller_desc, void* st
   xf_status s = xf::validate(caller_desc);
   if (s != XF_SUCCESS) return s;
   void* ws = nullptr;
-  s = static_workspace_address(&ws);
+  s = static_workspace_address(&ws, nullptr);
   if (s != XF_SUCCESS) return s;
   // The array is the whole workspace this call may use.  A schedule that needs more (a split of
   // the last wave whose partial accumulators do not fit) is refused by build_plan, not quietly

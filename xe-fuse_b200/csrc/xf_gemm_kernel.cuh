@@ -357,25 +357,48 @@ __device__ __forceinline__ int cos_sin_width(const EpiParams& e, int N) {
   return e.cos_sin_period > 0 ? e.cos_sin_period : N;
 }
 
+// Epilogue features a kernel instance is COMPILED with (template parameter EM).  The flat program is
+// still read at run time, but an instance only carries the code of the steps its mask names: the
+// epilogue of a CTA's last tile runs with nothing to hide behind, a few times per warp, and every
+// taken branch over code that is never executed costs it an instruction fetch from far away (a
+// minimal epilogue took 0.35 us less per 32-column slice than the all-in-one one).  The host picks
+// the smallest instance that covers a descriptor; row scale, column scale and bias are in all of them.
+enum : int {
+  EF_MAT = 1,     // full-matrix residual and the auxiliary (dual) output
+  EF_UNARY = 2,   // GeLU / SiLU / ... element-wise activations
+  EF_GLU = 4,     // SwiGLU / GeGLU pairs, also the compact [M, N/2] layout
+  EF_ROPE = 8,    // rotary pairs with a cos_sin operand
+  EF_MISC = 16,   // pair swap, fp32 / int32 outputs, per-thread (non-TMA) stores, row_sumsq side output
+  EF_ALL = 31
+};
+
 // Which full-matrix operand of the flat program is fetched ahead of the accumulator read.
 enum : int { PRE_NONE = 0, PRE_RESIDUAL = 1, PRE_COS_SIN = 2 };
+template <int EM>
 __device__ __forceinline__ int preload_choice(const EpiParams& e) {
-  return e.pair == PAIR_ROPE ? PRE_COS_SIN : (e.residual.enabled ? PRE_RESIDUAL : PRE_NONE);
+  if constexpr ((EM & EF_ROPE) != 0) {
+    if (e.pair == PAIR_ROPE) return PRE_COS_SIN;
+  }
+  if constexpr ((EM & EF_MAT) != 0) {
+    if (e.residual.enabled) return PRE_RESIDUAL;
+  }
+  return PRE_NONE;
 }
 
 // Asks L2 for this row's part of the full-matrix operands of tile columns [n0, n0 + ncols): issued
 // by the epilogue warps while the tile's main loop still runs, so the operand reads of the epilogue
 // proper hit L2 instead of waiting for HBM.  `part` of `nparts` warps that share the row.
+template <int EM>
 __device__ __forceinline__ void prefetch_tile_operands(const EpiParams& e, int N, int l, int row,
                                                        int n0, int ncols, int part, int nparts) {
-  if (e.residual.enabled) {
+  if ((EM & EF_MAT) && e.residual.enabled) {
     const int es = e.residual.dtype == DT_BF16 ? 2 : 4;
     const char* base = reinterpret_cast<const char*>(e.residual.ptr) +
                        (static_cast<long long>(l) * e.residual.batch_stride +
                         static_cast<long long>(row) * e.residual.ld + n0) * es;
     for (int off = part * 128; off < ncols * es; off += nparts * 128) ptx::prefetch_l2(base + off);
   }
-  if (e.pair == PAIR_ROPE) {
+  if ((EM & EF_ROPE) && e.pair == PAIR_ROPE) {
     const int width = cos_sin_width(e, N);
     int c0 = cos_sin_col(e, n0), nc = ncols;
     if (nc >= width) { c0 = 0; nc = width; }          // the tile walks the whole per-head table
@@ -422,7 +445,7 @@ __device__ __forceinline__ void rope_pair(float xe, float xo, float c, float s, 
   oo = -xe * s + xo * c;
 }
 
-template <int KIND>
+template <int KIND, int EM>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const uint32_t (&r)[32],
                                                float (&v)[32], int row, bool row_ok, int l,
                                                int gcol0, float rs, int pre_which, int pre_mode,
@@ -432,6 +455,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
   for (int i = 0; i < 32; ++i)
     v[i] = (KIND == 0) ? __uint_as_float(r[i]) : static_cast<float>(static_cast<int>(r[i]));
 
+  if constexpr ((EM & EF_MAT) != 0) {
   if (e.residual.enabled && row_ok) {
     if (staged != nullptr && pre_which == PRE_RESIDUAL) {
       const uint8_t* srow_ptr = staged + (scol >> 6) * 16384 + srow * 128;
@@ -480,6 +504,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
       store_bf16_row(ptr, pk, N - gcol0, 32);
     }
   }
+  }   // EF_MAT
   if (e.row_scale.enabled) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] *= rs;
@@ -488,6 +513,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
   if (e.bias.enabled) apply_vec32<false>(e.bias, l, gcol0, N, 0.0f, v);
   // The op switches sit OUTSIDE the element loops: every loop body is straight-line code, so the
   // 32 independent elements of a chunk interleave instead of running as one dependent chain each.
+  if constexpr ((EM & EF_UNARY) != 0) {
   switch (e.unary) {
     case UN_NONE: break;
 #define XF_UNARY_CASE(OP)                                      \
@@ -503,7 +529,8 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
 #undef XF_UNARY_CASE
     default: break;
   }
-  if (e.pair == PAIR_SWIGLU || e.pair == PAIR_GEGLU) {
+  }   // EF_UNARY
+  if ((EM & EF_GLU) && (e.pair == PAIR_SWIGLU || e.pair == PAIR_GEGLU)) {
     float o[16];
     if (e.pair == PAIR_SWIGLU) {
 #pragma unroll
@@ -521,7 +548,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
 #pragma unroll
       for (int j = 0; j < 16; ++j) { v[2 * j] = o[j]; v[2 * j + 1] = o[j]; }
     }
-  } else if (e.pair == PAIR_ROPE) {
+  } else if ((EM & EF_ROPE) && e.pair == PAIR_ROPE) {
     if (staged != nullptr && pre_which == PRE_COS_SIN && row_ok) {
       const uint8_t* srow_ptr = staged + (scol >> 5) * 16384 + srow * 128;
 #pragma unroll
@@ -553,7 +580,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
 #pragma unroll
       for (int j = 0; j < 16; ++j) rope_pair(v[2 * j], v[2 * j + 1], cs[2 * j], cs[2 * j + 1], v[2 * j], v[2 * j + 1]);
     }
-  } else if (e.pair == PAIR_SWAP) {
+  } else if ((EM & EF_MISC) && e.pair == PAIR_SWAP) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const float t = v[2 * j];
@@ -563,7 +590,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& e, int N, const 
   }
 }
 
-template <int KIND, int BN, int CTAS, int KS, int KC>
+template <int KIND, int BN, int CTAS, int KS, int KC, int EM>
 __global__ void __launch_bounds__(384, 1)
 gemm_evt_kernel(const __grid_constant__ GemmParams p) {
   using C = TileCfg<KIND, BN, CTAS, KS, KC>;
@@ -604,8 +631,8 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
 
   // The full-matrix epilogue operand of the CTA's last tile is staged in shared memory when one
   // tile of it fits a pipeline stage (and the variant keeps its idle stages free for it).
-  const bool tail_opnd = (KC == 1) && p.tail_opnd != 0 && p.tail_opnd_boxes * 16384 <= C::STAGE_BYTES &&
-                         STAGES >= 3;
+  const bool tail_opnd = (KC == 1) && (EM & (EF_MAT | EF_ROPE)) && p.tail_opnd != 0 &&
+                         p.tail_opnd_boxes * 16384 <= C::STAGE_BYTES && STAGES >= 3;
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tmap(&p.tm_a);
     ptx::prefetch_tmap(&p.tm_b);
@@ -828,12 +855,12 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
     bool res_failed = false;
     int kb_seen = 0;                        // K blocks this CTA's pipeline has carried so far
     const uint8_t* staged = nullptr;        // the last tile's operand tile in shared memory, if staged
-    const bool compact = e.compact != 0;
+    const bool compact = (EM & EF_GLU) ? e.compact != 0 : false;
     const int n_out = compact ? (p.N >> 1) : p.N;
     const int slices_per_unit = compact ? 2 : 1;   // 32 output columns = 1 or 2 accumulator slices
     const uint32_t tempty_leader =
         (CTAS == 2) ? ptx::mapa(ptx::smem_u32(&tempty_bar[0]), pair_base) : ptx::smem_u32(&tempty_bar[0]);
-    const int pre_which = preload_choice(e);
+    const int pre_which = preload_choice<EM>(e);
     int it = 0;
     for (int w = cluster_idx; w < total_items; w += num_clusters, ++it) {
       if (KC > 1 && it > 0) break;   // cluster split-K: one tile per cluster
@@ -866,8 +893,8 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       if (e.row_scale.enabled && row_ok && (!helper || shared3))
         rs = load_vec_elem(e.row_scale, static_cast<long long>(l) * e.row_scale.batch_stride + row);
       // while the tile's main loop runs: bring this row's residual / cos_sin lines into L2
-      if (!helper && row_ok && pre_which != PRE_NONE && p.d_dtype != DT_S32)
-        prefetch_tile_operands(e, p.N, l, row, n0, min(BN, p.N - n0), half, 2);
+      if ((EM & (EF_MAT | EF_ROPE)) && !helper && row_ok && pre_which != PRE_NONE && p.d_dtype != DT_S32)
+        prefetch_tile_operands<EM>(e, p.N, l, row, n0, min(BN, p.N - n0), half, 2);
 
       // Helpers wait on a barrier of their own that completes once, with the CTA's last
       // accumulator: the two-phase barriers of the accumulator buffers name a phase by one parity
@@ -895,9 +922,12 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       const int nsub = (ncols_tile + 31) / 32;            // 32-column accumulator slices
       const int nunits = (nsub + slices_per_unit - 1) / slices_per_unit;
       bool released = false;
+      const bool last_item = (w + num_clusters >= total_items) || KC > 1;
       auto release_tmem = [&]() {   // this warp has read its last slice of the accumulator buffer
         released = true;
-        if (helper) return;         // helpers only see the last tile: nobody waits for its buffer
+        // nobody waits for the buffer of the CTA's last item (helpers only ever see that one): its
+        // epilogue is not hidden by anything, and the cluster-scope release costs it ~0.5 us
+        if (helper || last_item) return;
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(buf * 8));
@@ -1017,16 +1047,15 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
       // processed, so the TMEM read latency is paid once per tile instead of once per slice.
       uint4 pre[8];
       // residual slices by TMA into the buffer the result will be stored from (bf16 TMA-store path only)
-      const bool res_by_tma = p.res_tma != 0 && pre_which == PRE_RESIDUAL && !use_staged && !compact &&
+      const bool res_by_tma = (EM & EF_MAT) && p.res_tma != 0 && pre_which == PRE_RESIDUAL && !use_staged && !compact &&
                               !p.direct_store && p.d_dtype == DT_BF16 && warp_rows_ok && !(p.diag & (4 | 8));
       // the auxiliary output through a staging buffer and a TMA store (same conditions as the D store)
-      const bool aux_by_tma = p.aux_tma != 0 && !compact && !p.direct_store && p.d_dtype == DT_BF16 &&
+      const bool aux_by_tma = (EM & EF_MAT) && p.aux_tma != 0 && !compact && !p.direct_store && p.d_dtype == DT_BF16 &&
                               warp_rows_ok && !(p.diag & (4 | 8));
       const bool acc_prefetch = part_base == nullptr && (pre_which == PRE_NONE || use_staged) && !(p.diag & 32);
       bool prefetched = false;
       for (int u = u_first; u < u_end; u += u_step) {
         uint32_t pk[16];
-        const bool last_unit = (u + u_step >= u_end);
         int out_col0 = 0;
         bool stored_direct = false;
 #pragma unroll 1
@@ -1048,9 +1077,9 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
                                   m0 + q * 32, l);
             }
           } else if (!acc_prefetch && !use_staged && row_ok && !(p.diag & 4) && p.d_dtype != DT_S32) {
-            if (pre_which == PRE_RESIDUAL)
+            if ((EM & EF_MAT) && pre_which == PRE_RESIDUAL)
               pre_mode = mat_row32_issue(e.residual, l, row, n0 + tcol0, p.N, pre);
-            else if (pre_which == PRE_COS_SIN)
+            else if ((EM & EF_ROPE) && pre_which == PRE_COS_SIN)
               pre_mode = mat_row32_issue(e.cos_sin, l, row, cos_sin_col(e, n0 + tcol0), cos_sin_width(e, p.N), pre);
           }
           if (part_base == nullptr) {
@@ -1134,7 +1163,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             }
           }
           if (p.diag & 4) { stored_direct = true; continue; }  // diagnostics: TMEM drain only
-          if (p.d_dtype == DT_S32) {
+          if ((EM & EF_MISC) && p.d_dtype == DT_S32) {
             // raw int32 accumulator, no epilogue steps (checked on the host)
             if (row_ok) {
               int* dp = reinterpret_cast<int*>(p.D) + static_cast<long long>(l) * p.batch_d +
@@ -1171,7 +1200,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             if (lane == 0) ptx::tma_store_wait_read<C::EPI_BUFS - 1>();
             __syncwarp();
           }
-          epilogue_chunk<KIND>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs, pre_which, pre_mode, pre,
+          epilogue_chunk<KIND, EM>(e, p.N, r, v, row, row_ok, l, n0 + tcol0, rs, pre_which, pre_mode, pre,
                                use_staged ? staged : nullptr, q * 32 + lane,
                                pre_which == PRE_RESIDUAL ? tcol0 : cos_sin_col(e, n0 + tcol0),
                                aux_by_tma ? stg + sidx * C::EPI_BUF_BYTES + lane * 64 : nullptr, (lane >> 1) & 3);
@@ -1186,7 +1215,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
             }
             sidx = (sidx + 1 == C::EPI_BUFS) ? 0 : sidx + 1;
           }
-          if (e.row_sumsq != nullptr) {
+          if ((EM & EF_MISC) && e.row_sumsq != nullptr) {
             // side output for a following RMSNorm: this row's sum of squares over these 32 columns
             const int nv = p.N - (n0 + tcol0);
             float ss = 0.0f;
@@ -1197,7 +1226,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
               e.row_sumsq[(static_cast<long long>(l) * units + ((n0 + tcol0) >> 5)) * p.M + row] = ss;
             }
           }
-          if (p.d_dtype == DT_F32) {
+          if ((EM & EF_MISC) && p.d_dtype == DT_F32) {
             if (row_ok) {
               float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(l) * p.batch_d +
                           static_cast<long long>(row) * p.ldd + n0 + tcol0;
@@ -1231,7 +1260,7 @@ gemm_evt_kernel(const __grid_constant__ GemmParams p) {
         }
         if (stored_direct || (p.diag & 8)) continue;
         // bf16 output: 32 output columns (64 bytes per row) per store
-        if (p.direct_store) {
+        if ((EM & EF_MISC) && p.direct_store) {
           if (row_ok) {
             __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) +
                                 static_cast<long long>(l) * p.batch_d +
