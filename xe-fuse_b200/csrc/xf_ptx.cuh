@@ -60,6 +60,12 @@ __device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
+// Arrival without memory ordering: for barriers that only order execution (what the other CTAs
+// must see was published by other means: fence.mbarrier_init for the barrier words, mbarrier
+// acquire/release for data).  The releasing form also waits for the CTA's outstanding stores.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
