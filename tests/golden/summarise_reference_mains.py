@@ -1,7 +1,7 @@
 """Condenses the log written by tests/test_reference_mains.py (XEFUSE_REFMAINS_LOG=<file>) into the
 verdict lines kept in tests/golden/reference_mains_b200.txt.
 
-Usage: python tests/golden/summarise_reference_mains.py <log> [<out>]
+Usage: python tests/golden/summarise_reference_mains.py <log> [<out> [<environment of the test run>]]
 
 The log holds the complete output of every reference program (tests/test_k*.cpp, the MoE examples,
 the generated kernels and pipelines of IntelLabs/Xe-Fuse, built unmodified by
@@ -12,7 +12,7 @@ import os
 import re
 import sys
 
-KEEP = re.compile(r"Disposition|Passed|FAILED|Failed|ALL PASS|SOME_FAILED|CORRECTNESS|Correctness|"
+KEEP = re.compile(r"Disposition|Passed|FAILED|Failed|PASS|FAIL|SOME_FAILED|CORRECTNESS|Correctness|"
                   r"compare: \d+ of \d+|max_rel_err")
 
 
@@ -35,9 +35,10 @@ if __name__ == "__main__":
                                                              "reference_mains_b200.txt")
     with open(src) as f:
         body = summarise(f.read())
+    env = (sys.argv[3] + " ") if len(sys.argv) > 3 else ""
     head = ("# Verdicts of the reference's own programs (IntelLabs/Xe-Fuse tests/, examples/, generated kernels and\n"
             "# pipelines; built unmodified against xe-fuse_b200/include by oracle/build_ref_mains.py) on one B200.\n"
-            "# Made by: XEFUSE_REFMAINS_LOG=<log> python -m pytest tests/test_reference_mains.py -m gpu\n"
+            f"# Made by: {env}XEFUSE_REFMAINS_LOG=<log> python -m pytest tests/test_reference_mains.py -m gpu\n"
             "#          python tests/golden/summarise_reference_mains.py <log>\n")
     with open(dst, "w") as f:
         f.write(head + body)
