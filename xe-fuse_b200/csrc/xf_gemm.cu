@@ -474,12 +474,22 @@ static xf_status plan_geometry(const xf_gemm_desc* d, Geometry* g) {
     return XF_ERR_NOT_SUPPORTED;
   }
   g->v = v; g->dev = dev; g->sm_count = sm_count;
-  for (int c = 0; c < EC_COUNT; ++c) {
-    cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel_of(*v, c)),
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem);
-    if (ce != cudaSuccess) {
-      set_error("cudaFuncSetAttribute(smem=%d) failed: %s", v->smem, cudaGetErrorString(ce));
-      return XF_ERR_INTERNAL;
+  {
+    // every class instance of the variant may use the variant's shared memory: set once per device
+    static std::mutex mu;
+    static bool done[64][sizeof(g_variants) / sizeof(g_variants[0])];
+    std::lock_guard<std::mutex> lock(mu);
+    const int vi = static_cast<int>(v - g_variants);
+    if (dev < 0 || dev >= 64 || !done[dev][vi]) {
+      for (int c = 0; c < EC_COUNT; ++c) {
+        cudaError_t ce = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel_of(*v, c)),
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, v->smem);
+        if (ce != cudaSuccess) {
+          set_error("cudaFuncSetAttribute(smem=%d) failed: %s", v->smem, cudaGetErrorString(ce));
+          return XF_ERR_INTERNAL;
+        }
+      }
+      if (dev >= 0 && dev < 64) done[dev][vi] = true;
     }
   }
   const int es = elem_size(d->dtype_ab);
