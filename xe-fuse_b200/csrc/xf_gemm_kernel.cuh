@@ -25,6 +25,10 @@
 // (st.shared::cluster into the partner's idle pipeline stages) and each pair finishes BN / KC of the
 // tile's columns.  No global scratch, no second launch.
 //
+// Every tile variant is compiled once per epilogue class (template parameter EM, a mask of EF_*
+// features): the flat epilogue program is read at run time, but an instance only carries the code
+// of the steps its mask names; the host launches the smallest class that covers a descriptor.
+//
 // Shared memory per stage: A 128 rows x 128 B (K-major, 128-B swizzle) and B as BN/CTAS columns
 // split into 128-B column groups of KBLK rows each (MN-major, 128-B swizzle), exactly as the TMA
 // boxes land.  With CTAS == 2 each CTA loads its own 128 rows of A and its own half of the B
