@@ -62,6 +62,11 @@ def build(force=False, verbose=False):
     if r.returncode != 0:
         sys.stderr.write(r.stdout)
         raise RuntimeError("link failed")
+    for o in objs:          # the objects are not reused: every stale build recompiles all sources
+        try:
+            os.remove(o)
+        except OSError:
+            pass
     return LIB
 
 
