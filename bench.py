@@ -905,7 +905,7 @@ def run_reference_arm(args, stages):
     if rank != 0:
         return
     steps, warm = args.steps, args.warmup
-    per_step = max(0.5, min(6.0, 150.0 / max(1, steps + warm)))
+    per_step = max(0.5, min(6.0, 120.0 / max(1, steps + warm)))   # CPU seconds of oracle work per step
     vals = []
     rows = cores = None
     cols = None
