@@ -420,9 +420,9 @@ class Workload:
                     raise SystemExit("bench.py: a kernel reported a bounded-wait timeout")
 
     def graph_of(self, n):
-        """A CUDA graph of `n` consecutive steps (single GPU, kernels only): a step of a small
-        workload lasts 20-40 us, about what a launch through Python costs, so its steps are
-        replayed from a graph instead of being launched one by one."""
+        """A CUDA graph of `n` consecutive steps of this rank (kernels only, no collective): a step
+        of a small workload lasts 20-90 us, the order of what a launch through Python costs, so its
+        steps are replayed from a graph instead of being launched one by one."""
         torch = self.torch
         s = torch.cuda.Stream(self.ctx["dev"])
         g = torch.cuda.CUDAGraph()
